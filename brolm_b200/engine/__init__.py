@@ -1,0 +1,5 @@
+from .context import StepContext
+from .model import DecoderModel, as_dtype, load_model, write_random_model
+from .step import Engine, StepError
+
+__all__ = ["StepContext", "DecoderModel", "as_dtype", "load_model", "write_random_model", "Engine", "StepError"]

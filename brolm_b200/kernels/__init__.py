@@ -1,0 +1,224 @@
+"""Python face of the hand-written CUDA kernels.
+
+Every function takes CUDA tensors, checks what the kernel cannot check itself,
+and launches on the current torch stream.  There is no CPU path and no
+library fallback: a missing build or a CPU tensor raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+from .build import KernelBuildError, build_all, load_library
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+_ERRORS = {
+    10001: "unsupported element type",
+    10002: "a size the kernel does not take",
+    10003: "a size beyond the kernel's limit",
+    10004: "a stride or pointer that is not aligned as the kernel needs",
+}
+ACTIVATIONS = {"gelu_tanh": 0, "gelu_pytorch_tanh": 0, "silu": 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"element type {t.dtype} is not float32 or bfloat16") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("brolm_b200 kernels run on CUDA tensors only; there is no CPU path")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status in _ERRORS:
+        raise KernelError(f"{what}: {_ERRORS[status]}")
+    raise KernelError(f"{what}: CUDA error {status}")
+
+
+_fn_cache: dict[str, ctypes._CFuncPtr] = {}
+
+
+def _fn(lib: str, name: str, argtypes: list) -> ctypes._CFuncPtr:
+    f = _fn_cache.get(name)
+    if f is None:
+        f = getattr(load_library(lib), name)
+        f.argtypes = argtypes
+        f.restype = c_int
+        _fn_cache[name] = f
+    return f
+
+
+# ---------------------------------------------------------------------------
+def embed_scale(ids: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Tensor) -> None:
+    """out[t] = float(table[ids[t]]) * scale;  ids int32, out float32 (tokens, hidden)."""
+    assert ids.dtype == torch.int32 and out.dtype == torch.float32 and table.is_contiguous() and out.is_contiguous()
+    f = _fn("core", "brolm_embed_scale", [c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(ids), _ptr(table), _code(table), scale, _ptr(out), ids.numel(), table.shape[1], _stream()),
+           "embed_scale")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * (offset + weight)."""
+    assert x.is_contiguous() and out.is_contiguous() and weight.is_contiguous()
+    n = out.shape[0]
+    hidden = x.shape[-1]
+    assert weight.numel() == hidden and out.shape[-1] == hidden
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.numel() == n
+    else:
+        assert x.shape[0] == n
+    f = _fn("core", "brolm_rmsnorm", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_int,
+                                      c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _code(x), _ptr(rows), _ptr(weight), _code(weight), eps, offset, _ptr(out), _code(out), n,
+             hidden, _stream()), "rmsnorm")
+
+
+def residual_rmsnorm(h: torch.Tensor, y: torch.Tensor, post_weight: Optional[torch.Tensor], post_eps: float,
+                     post_offset: float, next_weight: Optional[torch.Tensor], next_eps: float, next_offset: float,
+                     out: Optional[torch.Tensor]) -> None:
+    """h += rmsnorm(y; post) (or y when post_weight is None); out = rmsnorm(h; next) when next_weight is given."""
+    assert h.dtype == torch.float32 and h.is_contiguous() and y.is_contiguous() and y.shape == h.shape
+    wd = None
+    for w in (post_weight, next_weight):
+        if w is not None:
+            assert w.is_contiguous() and w.numel() == h.shape[-1]
+            if wd is not None and w.dtype != wd:
+                raise KernelError("residual_rmsnorm: both gains must have one element type")
+            wd = w.dtype
+    if next_weight is not None:
+        assert out is not None and out.is_contiguous() and out.shape == h.shape
+    f = _fn("core", "brolm_residual_rmsnorm", [c_void_p, c_void_p, c_int, c_void_p, c_float, c_float, c_void_p,
+                                               c_float, c_float, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(h), _ptr(y), _code(y), _ptr(post_weight), post_eps, post_offset, _ptr(next_weight), next_eps,
+             next_offset, _CODES[wd] if wd is not None else F32, _ptr(out) if next_weight is not None else None,
+             _code(out) if next_weight is not None else F32, h.shape[0], h.shape[-1], _stream()),
+           "residual_rmsnorm")
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, tok_seq: Optional[torch.Tensor],
+                  cos_sin: Optional[torch.Tensor], n_q: int, n_kv: int, head_dim: int, rotary_dim: int,
+                  k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                  page_table: Optional[torch.Tensor], kv_len: Optional[torch.Tensor], ring: int,
+                  page_size: int) -> None:
+    """Rotate q and k inside qkv (tokens, (n_q + 2 n_kv) * head_dim) and write k, v into the cache pages."""
+    assert qkv.is_contiguous() and qkv.shape[1] == (n_q + 2 * n_kv) * head_dim
+    assert positions.dtype == torch.int32 and positions.numel() == qkv.shape[0]
+    pt_stride = 0
+    if k_pages is not None:
+        assert v_pages is not None and page_table is not None and kv_len is not None and tok_seq is not None
+        assert k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype
+        assert k_pages.is_contiguous() and v_pages.is_contiguous()
+        assert tuple(k_pages.shape[1:]) == (n_kv, page_size, head_dim), (k_pages.shape, n_kv, page_size, head_dim)
+        assert page_table.dtype == torch.int32 and page_table.dim() == 2 and page_table.stride(1) == 1
+        assert kv_len.dtype == torch.int32 and tok_seq.dtype == torch.int32
+        pt_stride = page_table.stride(0)
+    if cos_sin is not None:
+        assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1:] == (rotary_dim // 2, 2)
+    f = _fn("core", "brolm_rope_kv_write", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                            c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                            c_void_p])
+    _check(f(_ptr(qkv), _code(qkv), _ptr(positions), _ptr(tok_seq), _ptr(cos_sin), n_q, n_kv, head_dim, rotary_dim,
+             _ptr(k_pages), _ptr(v_pages), _ptr(page_table), pt_stride, _ptr(kv_len), ring, page_size,
+             qkv.shape[0], _stream()), "rope_kv_write")
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out = act(gate) * up for gate_up = [gate | up] (tokens, 2 * inter)."""
+    assert gate_up.is_contiguous() and out.is_contiguous() and gate_up.dtype == out.dtype
+    assert gate_up.shape[1] == 2 * out.shape[1] and gate_up.shape[0] == out.shape[0]
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"gated_act: unknown activation '{activation}' (known: {sorted(ACTIVATIONS)})")
+    f = _fn("core", "brolm_gated_act", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(gate_up), _ptr(out), _code(out), out.shape[0], out.shape[1], ACTIVATIONS[activation], _stream()),
+           "gated_act")
+
+
+def softcap(x: torch.Tensor, out: torch.Tensor, cap: float) -> None:
+    """out (float32) = cap * tanh(x / cap); cap <= 0 only converts."""
+    assert x.is_contiguous() and out.is_contiguous() and out.dtype == torch.float32 and x.numel() == out.numel()
+    f = _fn("core", "brolm_softcap", [c_void_p, c_int, c_void_p, c_longlong, c_float, c_void_p])
+    _check(f(_ptr(x), _code(x), _ptr(out), x.numel(), cap, _stream()), "softcap")
+
+
+def linear_f32(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out (M, N) = x (M, K) @ weight (N, K)^T, all float32, rows may be strided."""
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32 and out.dtype == torch.float32
+    assert x.dim() == 2 and weight.dim() == 2 and out.dim() == 2
+    assert x.stride(1) == 1 and weight.stride(1) == 1 and out.stride(1) == 1
+    M, K = x.shape
+    N = weight.shape[0]
+    assert weight.shape[1] == K and tuple(out.shape) == (M, N)
+    f = _fn("linear_f32", "brolm_linear_f32", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                               c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K, _stream()),
+           "linear_f32")
+
+
+def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor, *, n_kv: int,
+                   group: int, head_dim: int, scale: float, cap: float, window: int, batch: int, max_q_len: int,
+                   k: Optional[torch.Tensor] = None, v: Optional[torch.Tensor] = None,
+                   k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
+                   page_table: Optional[torch.Tensor] = None, ring: int = 0, page_size: int = 0) -> None:
+    """Exact attention on CUDA cores.  Keys come from (k, v) packed like q, or from cache pages."""
+    assert q.stride(-1) == 1 and out.stride(-1) == 1 and q.dtype == out.dtype
+    assert cu_q.dtype == torch.int32 and kv_len.dtype == torch.int32
+    kv_stride = pt_stride = 0
+    if k_pages is not None:
+        assert page_table is not None and page_table.dtype == torch.int32 and page_table.stride(1) == 1
+        assert k_pages.dtype == q.dtype and v_pages.dtype == q.dtype and k_pages.is_contiguous() and v_pages.is_contiguous()
+        assert tuple(k_pages.shape[1:]) == (n_kv, page_size, head_dim)
+        pt_stride = page_table.stride(0)
+    else:
+        assert k is not None and v is not None and k.dtype == q.dtype and v.dtype == q.dtype
+        assert k.stride(-1) == 1 and v.stride(-1) == 1 and k.stride(0) == v.stride(0)
+        kv_stride = k.stride(0)
+    f = _fn("attn_simt", "brolm_attn_simt", [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                             c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_void_p])
+    _check(f(_code(q), _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cu_q), _ptr(kv_len), _ptr(k), _ptr(v),
+             kv_stride, _ptr(k_pages), _ptr(v_pages), _ptr(page_table), pt_stride, ring, page_size, n_kv, group,
+             head_dim, scale, cap, window, batch, max_q_len, _stream()), "attention_simt")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] (int32) = first index of the maximum of logits[r] (float32)."""
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and out.dtype == torch.int32
+    f = _fn("sampling", "brolm_argmax", [c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(logits), logits.shape[0], logits.shape[1], _ptr(out), _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int, streams: torch.Tensor,
+           counter: int, out: torch.Tensor) -> None:
+    """One draw per row from softmax(logits / temperature) after top-k and top-p."""
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    assert streams.dtype == torch.int32 and out.dtype == torch.int32 and streams.numel() == logits.shape[0]
+    f = _fn("sampling", "brolm_sample", [c_void_p, c_int, c_int, c_float, c_int, c_float, c_ulonglong, c_void_p,
+                                         c_ulonglong, c_void_p, c_void_p])
+    _check(f(_ptr(logits), logits.shape[0], logits.shape[1], temperature, top_k, top_p, seed & (2 ** 64 - 1),
+             _ptr(streams), counter, _ptr(out), _stream()), "sample")
+
+
+__all__ = ["KernelBuildError", "KernelError", "build_all", "embed_scale", "rmsnorm", "residual_rmsnorm",
+           "rope_kv_write", "gated_act", "softcap", "linear_f32", "attention_simt", "argmax", "sample"]

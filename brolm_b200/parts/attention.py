@@ -1,0 +1,94 @@
+"""The attention mixer: grouped-query attention with rotary positions, a
+score scale of its own, tanh soft-capping of the scores and an optional
+sliding window, over a paged cache.
+
+Formulas as wlejon/brolm computes them (src/gemma2.cpp:349-369): fused q/k/v
+projection without bias, rotation of q and k at the absolute position, k and
+v into the cache, scores = q.k * scale -> cap * tanh(./cap) -> causal/window
+mask -> softmax, then the output projection.  Key j is visible from position
+p iff 0 <= p - j < window.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import kernels
+from ..cache import KVSpec
+from .base import ParamSpec, Part, register_part
+from .linear import linear
+
+
+class Attention(Part):
+    kind = "mixer"
+
+    def __init__(self, hidden: int, n_q: int, n_kv: int, head_dim: int, scale: float, softcap: float = 0.0,
+                 window: Optional[int] = None, position: Optional[Part] = None):
+        if n_q % n_kv:
+            raise ValueError("attention: the number of query heads must be a multiple of the kv heads")
+        if head_dim % 16:
+            raise ValueError(f"attention: head_dim {head_dim} is not a multiple of 16; the kernels refuse it")
+        if head_dim > 512:
+            raise ValueError(f"attention: head_dim {head_dim} is beyond the kernels' limit of 512")
+        self.hidden, self.n_q, self.n_kv, self.head_dim = hidden, n_q, n_kv, head_dim
+        self.scale, self.softcap = float(scale), float(softcap or 0.0)
+        self.window = int(window) if window else None
+        self.position = position
+        self.q_dim, self.kv_dim = n_q * head_dim, n_kv * head_dim
+
+    def param_specs(self):
+        return {"q": ParamSpec((self.q_dim, self.hidden)), "k": ParamSpec((self.kv_dim, self.hidden)),
+                "v": ParamSpec((self.kv_dim, self.hidden)), "o": ParamSpec((self.hidden, self.q_dim))}
+
+    def bind(self, params):
+        # one projection for q, k and v: rows [Wq; Wk; Wv]
+        kinds = {params[n].dtype for n in ("q", "k", "v")}
+        dt = torch.float32 if (len(kinds) > 1 or torch.float32 in kinds) else next(iter(kinds))
+        self.w_qkv = torch.cat([params["q"].to(dt), params["k"].to(dt), params["v"].to(dt)], dim=0).contiguous()
+        self.w_o = params["o"]
+        self.params = {}
+
+    def cache_spec(self):
+        return KVSpec(self.n_kv, self.head_dim, self.window)
+
+    def prepare(self, max_positions, device):
+        if self.position is not None:
+            self.position.prepare(max_positions, device)
+
+    def forward(self, x: torch.Tensor, ctx, entry, writes_cache: bool = True) -> torch.Tensor:
+        """x (tokens, hidden) in the step's element type -> (tokens, hidden) float32."""
+        qkv = linear(x, self.w_qkv, out_dtype=ctx.dtype)
+        k_pages, v_pages, table, ring, page = ctx.kv(entry)
+        rot = self.position.rotary_dim if self.position is not None else 0
+        kernels.rope_kv_write(
+            qkv, ctx.positions, ctx.tok_seq, self.position.table if self.position is not None else None,
+            self.n_q, self.n_kv, self.head_dim, rot,
+            k_pages if writes_cache else None, v_pages if writes_cache else None, table, ctx.kv_len, ring, page)
+        q = qkv[:, :self.q_dim]
+        out = torch.empty((qkv.shape[0], self.q_dim), dtype=ctx.dtype, device=x.device)
+        common = dict(n_kv=self.n_kv, group=self.n_q // self.n_kv, head_dim=self.head_dim, scale=self.scale,
+                      cap=self.softcap, window=self.window or 0, batch=ctx.batch, max_q_len=ctx.max_q_len)
+        if ctx.mode == "prefill" and writes_cache:
+            # the step's own keys and values, still packed: a prompt longer than
+            # the window needs keys the ring no longer holds
+            k = qkv[:, self.q_dim:self.q_dim + self.kv_dim]
+            v = qkv[:, self.q_dim + self.kv_dim:]
+            self.attend_packed(q, k, v, out, ctx, common)
+        else:
+            if ctx.mode == "prefill" and self.window and max(ctx.host_lengths) > ring:
+                raise NotImplementedError("a layer that reads another layer's windowed cache cannot take a "
+                                          "prompt longer than the ring in one step")
+            self.attend_paged(q, out, ctx, common, k_pages, v_pages, table, ring, page)
+        return linear(out, self.w_o, out_dtype=torch.float32)
+
+    # the two attention calls are methods so that a faster kernel can take them over
+    def attend_packed(self, q, k, v, out, ctx, common):
+        kernels.attention_simt(q, out, ctx.cu_q, ctx.kv_len, k=k, v=v, **common)
+
+    def attend_paged(self, q, out, ctx, common, k_pages, v_pages, table, ring, page):
+        kernels.attention_simt(q, out, ctx.cu_q, ctx.kv_len, k_pages=k_pages, v_pages=v_pages, page_table=table,
+                               ring=ring, page_size=page, **common)
+
+
+register_part("mixer", "attention", Attention)

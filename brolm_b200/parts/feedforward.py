@@ -1,0 +1,42 @@
+"""Feed-forward parts."""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from .base import ParamSpec, Part, register_part
+from .linear import linear
+
+
+class GatedFeedForward(Part):
+    """down(act(gate(x)) * up(x)), dense, no bias
+    (wlejon/brolm src/gemma2.cpp:378-382 with act = gelu, tanh form).
+    Gate and up run as one product over the rows [Wg; Wu]."""
+
+    kind = "feedforward"
+
+    def __init__(self, hidden: int, inter: int, activation: str = "gelu_tanh"):
+        if activation not in kernels.ACTIVATIONS:
+            raise ValueError(f"feed-forward: unknown activation '{activation}'")
+        self.hidden, self.inter, self.activation = hidden, inter, activation
+
+    def param_specs(self):
+        return {"gate": ParamSpec((self.inter, self.hidden)), "up": ParamSpec((self.inter, self.hidden)),
+                "down": ParamSpec((self.hidden, self.inter))}
+
+    def bind(self, params):
+        kinds = {params[n].dtype for n in ("gate", "up")}
+        dt = torch.float32 if (len(kinds) > 1 or torch.float32 in kinds) else next(iter(kinds))
+        self.w_gate_up = torch.cat([params["gate"].to(dt), params["up"].to(dt)], dim=0).contiguous()
+        self.w_down = params["down"]
+        self.params = {}
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        """x (tokens, hidden) -> (tokens, hidden) float32."""
+        gate_up = linear(x, self.w_gate_up, out_dtype=ctx.dtype)
+        act = torch.empty((x.shape[0], self.inter), dtype=ctx.dtype, device=x.device)
+        kernels.gated_act(gate_up, act, self.activation)
+        return linear(act, self.w_down, out_dtype=torch.float32)
+
+
+register_part("feedforward", "gated", GatedFeedForward)

@@ -1,0 +1,43 @@
+"""Matrix products  Y = X W^T  with W stored (out, in), no bias
+(wlejon/brolm include/brolm/detail/compute.h:49-86 dispatches on the weight's
+element type in the same way).
+
+* float32 weight: the framework's own CUDA-core kernel, true 32-bit.
+* bfloat16 weight: the library product (cuBLAS through torch), float32
+  accumulation; the result is bfloat16 or, on request, float32.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import kernels
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    M = x.shape[0]
+    N = weight.shape[0]
+    if weight.dtype == torch.float32:
+        x32 = x if x.dtype == torch.float32 else x.float()
+        want = out_dtype or x.dtype
+        y = out if (out is not None and out.dtype == torch.float32) else \
+            torch.empty((M, N), dtype=torch.float32, device=x.device)
+        kernels.linear_f32(x32, weight, y)
+        if want != torch.float32:
+            y = y.to(want)
+            if out is not None:
+                out.copy_(y)
+                return out
+        return y
+    if weight.dtype == torch.bfloat16:
+        if x.dtype != torch.bfloat16:
+            x = x.to(torch.bfloat16)
+        want = out_dtype or torch.bfloat16
+        if want == torch.bfloat16:
+            return torch.mm(x, weight.t(), out=out) if out is not None else torch.mm(x, weight.t())
+        if out is not None:
+            return torch.mm(x, weight.t(), out_dtype=want, out=out)
+        return torch.mm(x, weight.t(), out_dtype=want)
+    raise TypeError(f"linear: weights of type {weight.dtype} are not supported")
