@@ -11,11 +11,13 @@ Public face, in the manner of wlejon/brolm's C++ API
 """
 from . import models  # noqa: F401  (registers the architectures)
 from .config import ConfigError, Gemma2Config, ModelConfig, load_config, register_architecture
-from .engine import DecoderModel, Engine, StepError, load_model, write_random_model
+from .engine import DecoderModel, Engine, StepError, generate, load_model, write_random_model
 from .parts import register_part
+from .sampling import GenerateOptions, SamplingParams, Sampler
 from .weights import WeightsError
 
 Model = DecoderModel
 
 __all__ = ["ConfigError", "Gemma2Config", "ModelConfig", "load_config", "register_architecture", "DecoderModel",
-           "Model", "Engine", "StepError", "load_model", "write_random_model", "register_part", "WeightsError"]
+           "Model", "Engine", "StepError", "load_model", "write_random_model", "register_part", "WeightsError", "generate", "GenerateOptions", "SamplingParams",
+           "Sampler"]

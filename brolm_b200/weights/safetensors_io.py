@@ -12,6 +12,7 @@ import json
 import mmap
 import os
 import struct
+import warnings
 from typing import Iterable, Iterator
 
 import torch
@@ -88,8 +89,10 @@ class SafetensorsFile:
         dtype, shape, begin, end = self.entries[name]
         if end == begin:
             return torch.empty(shape, dtype=dtype)
-        flat = torch.frombuffer(self._map, dtype=dtype, count=(end - begin) // dtype.itemsize,
-                                offset=self._base + begin)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)      # the map is read-only; nothing here writes to it
+            flat = torch.frombuffer(self._map, dtype=dtype, count=(end - begin) // dtype.itemsize,
+                                    offset=self._base + begin)
         return flat.reshape(shape)
 
 

@@ -1,0 +1,179 @@
+"""The engine against the plain implementation, in float32 and in bfloat16:
+whole requests, the last 32 tokens one by one, batches of unequal lengths
+whose shorter requests end earlier (batch after batch, so that slots and pages
+are used again), long decoding past the window's ring, the first tokens of a
+sequence, and greedy generation through the entry point."""
+import pytest
+import torch
+
+import brolm_b200 as bb
+from tests.helpers import TINY, make_folder, oracle_inputs, random_prompts
+from tests.plain import gemma2_plain as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+# Largest absolute error of a logit against the float64 oracle.  float32: the
+# bar wlejon/brolm sets for its own float path (tests/test_gemma2.cpp:247-248).
+# bfloat16: activations and weights carry 8 bits; the tiny models' logits are
+# of order 1 and the measured error is a few 1e-3.
+TOL = {"float32": 1e-4, "bfloat16": 3e-2}
+STORE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+CASES = [(name, dtype) for name in ("A", "B") for dtype in ("float32", "bfloat16")]
+
+
+@pytest.fixture(scope="module")
+def setups(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("models")
+    out = {}
+    for name, dtype in CASES:
+        folder = make_folder(tmp, name, STORE[dtype])
+        config, weights = oracle_inputs(folder)
+        model = bb.load_model(folder, dtype=dtype, device=DEV)
+        out[(name, dtype)] = (folder, config, weights, model)
+    return out
+
+
+def check(got, ref, dtype, what):
+    err = float((got.double().cpu() - ref).abs().max())
+    assert err <= TOL[dtype], f"{what}: error {err:.3e} exceeds {TOL[dtype]:.0e}"
+    return err
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_whole_requests(setups, name, dtype):
+    _, config, weights, model = setups[(name, dtype)]
+    eng = bb.Engine(model, max_tokens=512)
+    for p in random_prompts(config["vocab_size"], [1, 5, 64, 65, 150], seed=11):
+        ref = plain.forward(config, weights, p)
+        (s,) = eng.open(1)
+        got = eng.step([s], [p], want=[list(range(len(p)))])
+        check(got, ref, dtype, f"whole request of {len(p)}")
+        assert float(got.abs().max()) <= config["final_logit_softcapping"]
+        eng.close([s])
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_last_32_tokens_one_by_one(setups, name, dtype):
+    _, config, weights, model = setups[(name, dtype)]
+    eng = bb.Engine(model, max_tokens=512)
+    for p in random_prompts(config["vocab_size"], [40, 100, 170], seed=12):
+        ref = plain.forward(config, weights, p)
+        (s,) = eng.open(1)
+        n = len(p) - 32
+        got = eng.step([s], [p[:n]], want=[list(range(n))])
+        check(got, ref[:n], dtype, "prompt part")
+        for i in range(n, len(p)):
+            got = eng.step([s], [[p[i]]])
+            check(got[0], ref[i], dtype, f"token {i} of {len(p)} decoded alone")
+        eng.close([s])
+
+
+def run_batch_teacher_forced(eng, config, weights, prompts, prefill, dtype):
+    """Prefill ``prefill[i]`` tokens of each prompt together, then feed each
+    request's own next token; a request that runs out leaves the batch."""
+    refs = [plain.forward(config, weights, p) for p in prompts]
+    slots = eng.open(len(prompts))
+    got = eng.step(slots, [p[:k] for p, k in zip(prompts, prefill)], want=[list(range(k)) for k in prefill])
+    off = 0
+    for r, k in zip(refs, prefill):
+        check(got[off:off + k], r[:k], dtype, "batched prompt")
+        off += k
+    done = list(prefill)
+    live = [i for i in range(len(prompts)) if done[i] < len(prompts[i])]
+    for i in range(len(prompts)):
+        if i not in live:
+            eng.close([slots[i]])
+    while live:
+        got = eng.step([slots[i] for i in live], [[prompts[i][done[i]]] for i in live])
+        for row, i in enumerate(live):
+            check(got[row], refs[i][done[i]], dtype, f"request {i} token {done[i]} in a batch of {len(live)}")
+            done[i] += 1
+        for i in live:
+            if done[i] >= len(prompts[i]):
+                eng.close([slots[i]])
+        live = [i for i in live if done[i] < len(prompts[i])]
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_unequal_batches_one_after_another(setups, name, dtype):
+    _, config, weights, model = setups[(name, dtype)]
+    # room for one batch at a time only: the second and third batch must reuse slots and pages
+    eng = bb.Engine(model, max_tokens=64 * 8, max_slots=4)
+    V = config["vocab_size"]
+    run_batch_teacher_forced(eng, config, weights, random_prompts(V, [9, 100, 40, 150], 21), [5, 90, 1, 140], dtype)
+    assert eng.cache.live_slots == 0
+    run_batch_teacher_forced(eng, config, weights, random_prompts(V, [130, 3, 70, 66], 22), [120, 3, 64, 30], dtype)
+    run_batch_teacher_forced(eng, config, weights, random_prompts(V, [33, 34], 23), [1, 2], dtype)
+    assert eng.cache.live_slots == 0
+    assert all(g.pool.held_pages == 0 for g in eng.cache.kv_groups)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_long_decoding_from_a_short_prompt(setups, name, dtype):
+    _, config, weights, model = setups[(name, dtype)]
+    eng = bb.Engine(model, max_tokens=512)
+    p = random_prompts(config["vocab_size"], [210], seed=31)[0]
+    ref = plain.forward(config, weights, p)
+    (s,) = eng.open(1)
+    got = eng.step([s], [p[:1]])
+    check(got[0], ref[0], dtype, "first token")
+    for i in range(1, len(p)):
+        got = eng.step([s], [[p[i]]])
+        check(got[0], ref[i], dtype, f"token {i}")
+    eng.close([s])
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_padding_changes_nothing(setups, name, dtype):
+    """The same request gives the same logits alone and beside others of any length."""
+    _, config, weights, model = setups[(name, dtype)]
+    eng = bb.Engine(model, max_tokens=1024)
+    ps = random_prompts(config["vocab_size"], [70, 3, 129], seed=41)
+    (s,) = eng.open(1)
+    alone = eng.step([s], [ps[0]], want=[list(range(70))]).clone()
+    eng.close([s])
+    slots = eng.open(3)
+    together = eng.step(slots, ps, want=[list(range(70)), [], [128]])
+    eng.close(slots)
+    if dtype == "float32":
+        assert torch.equal(alone, together[:70])
+    else:
+        assert float((alone - together[:70]).abs().max()) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_greedy_generation_through_the_entry_point(setups, name, dtype):
+    _, config, weights, model = setups[(name, dtype)]
+    eng = bb.Engine(model, max_tokens=64 * 6, max_slots=3)
+    prompts = random_prompts(config["vocab_size"], [5, 11, 17, 1, 70], seed=51)
+    opts = bb.GenerateOptions(max_new_tokens=8, sampling=bb.SamplingParams(temperature=0.0), stop_on_eos=False)
+    outs = bb.generate(eng, prompts, eos_id=-1, opts=opts)
+    assert eng.cache.live_slots == 0
+    for p, o in zip(prompts, outs):
+        assert len(o) == 8
+        if dtype == "float32":
+            assert o == plain.greedy(config, weights, p, 8)
+        else:
+            # bfloat16 may pick another of two near-equal logits: the pick must be the oracle's
+            # maximum within the tolerance, given the tokens generated so far
+            ids = list(p)
+            for tok in o:
+                row = plain.forward(config, weights, ids)[-1]
+                assert float(row.max() - row[tok]) <= 2 * TOL[dtype]
+                ids.append(tok)
+
+
+def test_step_refuses_a_mixed_batch(setups):
+    _, config, weights, model = setups[("A", "float32")]
+    eng = bb.Engine(model, max_tokens=256)
+    a, b = eng.open(2)
+    eng.step([a], [[1, 2, 3]])
+    with pytest.raises(bb.StepError):
+        eng.step([a, b], [[4], [5, 6]])
+    with pytest.raises(bb.StepError):
+        eng.step([a], [[4, 5]])
+    with pytest.raises(bb.StepError):
+        eng.step([b], [[config["vocab_size"]]])
+    eng.close([a, b])

@@ -1,0 +1,345 @@
+"""Each kernel alone against a plain float64 torch restatement, at sizes
+other than the engine's (widths and vocabularies that are no power of two,
+head sizes in steps of 16, odd head counts)."""
+import math
+
+import pytest
+import torch
+
+from brolm_b200 import kernels
+from tests.plain import gemma2_plain as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = {torch.float32: 2e-6, torch.bfloat16: 8e-3}   # relative to the largest magnitude of the result
+
+
+def close(got, ref, dtype, scale=None):
+    ref = ref.double().cpu()
+    got = got.double().cpu()
+    s = scale if scale is not None else max(1e-30, float(ref.abs().max()))
+    err = float((got - ref).abs().max()) / s
+    assert err <= TOL[dtype], f"error {err:.3e} exceeds {TOL[dtype]:.1e}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_scale(dtype):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(1000, 200, generator=g).to(dtype)
+    ids = torch.randint(0, 1000, (37,), generator=g, dtype=torch.int32)
+    out = torch.empty(37, 200, dtype=torch.float32, device=DEV)
+    kernels.embed_scale(ids.to(DEV), table.to(DEV), math.sqrt(200.0), out)
+    ref = plain.embed(table, ids, 200)
+    close(out, ref, torch.float32)
+
+
+@pytest.mark.parametrize("xd,wd,od", [(torch.float32, torch.float32, torch.float32),
+                                       (torch.float32, torch.bfloat16, torch.bfloat16),
+                                       (torch.bfloat16, torch.float32, torch.bfloat16),
+                                       (torch.float32, torch.float32, torch.bfloat16)])
+@pytest.mark.parametrize("hidden", [200, 2304])
+def test_rmsnorm(xd, wd, od, hidden):
+    g = torch.Generator().manual_seed(1)
+    x = (torch.randn(19, hidden, generator=g) * 3).to(xd)
+    w = (torch.randn(hidden, generator=g) * 0.1).to(wd)
+    out = torch.empty(19, hidden, dtype=od, device=DEV)
+    kernels.rmsnorm(x.to(DEV), w.to(DEV), 1e-5, 1.0, out)
+    close(out, plain.rms_norm(x, w, 1e-5), od)
+    rows = torch.tensor([18, 0, 7], dtype=torch.int32)
+    out2 = torch.empty(3, hidden, dtype=od, device=DEV)
+    kernels.rmsnorm(x.to(DEV), w.to(DEV), 1e-5, 1.0, out2, rows.to(DEV))
+    close(out2, plain.rms_norm(x[rows.long()], w, 1e-5), od)
+
+
+@pytest.mark.parametrize("yd,wd,od", [(torch.float32, torch.float32, torch.float32),
+                                       (torch.float32, torch.bfloat16, torch.bfloat16),
+                                       (torch.bfloat16, torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("post,nxt", [(True, True), (True, False), (False, True), (False, False)])
+def test_residual_rmsnorm(yd, wd, od, post, nxt):
+    hidden = 328
+    g = torch.Generator().manual_seed(2)
+    h = torch.randn(11, hidden, generator=g) * 5
+    y = (torch.randn(11, hidden, generator=g) * 2).to(yd)
+    w1 = (torch.randn(hidden, generator=g) * 0.1).to(wd)
+    w2 = (torch.randn(hidden, generator=g) * 0.1).to(wd)
+    hd = h.clone().to(DEV)
+    out = torch.empty(11, hidden, dtype=od, device=DEV) if nxt else None
+    kernels.residual_rmsnorm(hd, y.to(DEV), w1.to(DEV) if post else None, 1e-6, 1.0,
+                             w2.to(DEV) if nxt else None, 1e-5, 1.0, out)
+    h_ref = h.double() + (plain.rms_norm(y, w1, 1e-6) if post else y.double())
+    close(hd, h_ref, torch.float32)
+    if nxt:
+        close(out, plain.rms_norm(h_ref, w2, 1e-5), od)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+def test_gated_act(dtype, act):
+    g = torch.Generator().manual_seed(3)
+    gu = (torch.randn(7, 2 * 330, generator=g) * 3).to(dtype)
+    out = torch.empty(7, 330, dtype=dtype, device=DEV)
+    kernels.gated_act(gu.to(DEV), out, act)
+    gate, up = gu[:, :330].double(), gu[:, 330:].double()
+    ref = (plain.gelu_tanh(gate) if act == "gelu_tanh" else gate * torch.sigmoid(gate)) * up
+    close(out, ref, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_softcap(dtype):
+    g = torch.Generator().manual_seed(4)
+    x = (torch.randn(3, 1001, generator=g) * 40).to(dtype)
+    out = torch.empty(3, 1001, dtype=torch.float32, device=DEV)
+    kernels.softcap(x.to(DEV), out, 30.0)
+    close(out, plain.soft_cap(x.double(), 30.0), torch.float32)
+    assert float(out.abs().max()) <= 30.0
+    kernels.softcap(x.to(DEV), out, 0.0)
+    close(out, x.double(), torch.float32)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 130, 96), (65, 200, 330), (128, 64, 16), (17, 1000, 203)])
+def test_linear_f32(M, N, K):
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(M, K, generator=g)
+    w = torch.randn(N, K, generator=g)
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    kernels.linear_f32(x.to(DEV), w.to(DEV), out)
+    close(out, plain.linear(x, w), torch.float32)
+    # a row gives the same bits alone and in the batch
+    one = torch.empty(1, N, dtype=torch.float32, device=DEV)
+    kernels.linear_f32(x[M - 1:M].to(DEV), w.to(DEV), one)
+    assert torch.equal(one[0], out[M - 1])
+
+
+def test_linear_f32_strided_views():
+    g = torch.Generator().manual_seed(6)
+    big = torch.randn(9, 3 * 48, generator=g).to(DEV)
+    w = torch.randn(20, 48, generator=g).to(DEV)
+    out = torch.zeros(9, 64, dtype=torch.float32, device=DEV)
+    kernels.linear_f32(big[:, 48:96], w, out[:, 8:28])
+    close(out[:, 8:28], plain.linear(big[:, 48:96].cpu(), w.cpu()), torch.float32)
+    assert float(out[:, :8].abs().max()) == 0 and float(out[:, 28:].abs().max()) == 0
+
+
+def _rope_case(dtype, n_q, n_kv, hd, ring, page, lengths, seed):
+    """Prompt pass of unequal sequences: rotation against the oracle and the pages written."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(lengths)
+    T = sum(lengths)
+    width = (n_q + 2 * n_kv) * hd
+    qkv = torch.randn(T, width, generator=g).to(dtype)
+    positions = torch.cat([torch.arange(n) for n in lengths]).int()
+    tok_seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lengths)]).int()
+    theta = 1000.0
+    half = hd // 2
+    inv = torch.tensor(theta, dtype=torch.float64) ** (-2.0 * torch.arange(half, dtype=torch.float64) / hd)
+    ang = torch.arange(max(lengths), dtype=torch.float64)[:, None] * inv[None]
+    table = torch.stack([ang.cos(), ang.sin()], -1).float()
+    pages_per = [min((n + page - 1) // page, ring // page) for n in lengths]
+    n_pages = sum(pages_per) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()        # scattered page ids
+    pt = torch.zeros(B, max(pages_per), dtype=torch.int32)
+    it = iter(perm)
+    for b in range(B):
+        for j in range(pages_per[b]):
+            pt[b, j] = next(it)
+    kp = torch.zeros(n_pages, n_kv, page, hd, dtype=dtype, device=DEV)
+    vp = torch.zeros_like(kp)
+    dq = qkv.clone().to(DEV)
+    kernels.rope_kv_write(dq, positions.to(DEV), tok_seq.to(DEV), table.to(DEV), n_q, n_kv, hd, hd, kp, vp,
+                          pt.to(DEV), torch.tensor(lengths, dtype=torch.int32, device=DEV), ring, page)
+    q_ref = plain.rope(qkv[:, :n_q * hd], positions, hd, theta)
+    k_ref = plain.rope(qkv[:, n_q * hd:(n_q + n_kv) * hd], positions, hd, theta)
+    close(dq[:, :n_q * hd], q_ref, dtype)
+    close(dq[:, n_q * hd:(n_q + n_kv) * hd], k_ref, dtype)
+    assert torch.equal(dq[:, (n_q + n_kv) * hd:].cpu(), qkv[:, (n_q + n_kv) * hd:])
+    kp, vp, dq = kp.cpu(), vp.cpu(), dq.cpu()
+    t = 0
+    for b, n in enumerate(lengths):
+        for p in range(n):
+            if p >= n - ring:
+                ridx = p % ring
+                pg = int(pt[b, ridx // page])
+                assert torch.equal(kp[pg, :, ridx % page, :].reshape(-1), dq[t, n_q * hd:(n_q + n_kv) * hd]), (b, p)
+                assert torch.equal(vp[pg, :, ridx % page, :].reshape(-1), dq[t, (n_q + n_kv) * hd:]), (b, p)
+            t += 1
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_kv_write_all_keys(dtype):
+    _rope_case(dtype, n_q=6, n_kv=3, hd=48, ring=1 << 30, page=64, lengths=[1, 70, 130], seed=7)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_kv_write_ring(dtype):
+    # prompts longer than the ring: only the last `ring` places are written, each exactly once
+    _rope_case(dtype, n_q=2, n_kv=1, hd=32, ring=64, page=32, lengths=[200, 64, 65, 3], seed=8)
+
+
+def test_rope_skips_padding_rows():
+    qkv = torch.randn(4, 4 * 16).to(DEV)
+    before = qkv.clone()
+    table = torch.zeros(8, 8, 2)
+    table[..., 1] = 1.0   # a quarter turn everywhere
+    pos = torch.tensor([-1, 2, -1, 3], dtype=torch.int32, device=DEV)
+    kernels.rope_kv_write(qkv, pos, None, table.to(DEV), 2, 1, 16, 16, None, None, None, None, 64, 64)
+    assert torch.equal(qkv[0], before[0]) and torch.equal(qkv[2], before[2])
+    assert not torch.equal(qkv[1, :48], before[1, :48])
+
+
+# ---------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------
+def _attention_oracle(q, k, v, n_q, n_kv, hd, scale, cap, window):
+    return plain.attention(q, k, v, n_q, n_kv, hd, scale, cap, window)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_q,n_kv,hd,window,cap", [(4, 2, 16, 8, 50.0), (6, 1, 32, 16, 20.0), (3, 3, 48, 0, 0.0),
+                                                    (8, 4, 256, 100, 50.0), (5, 5, 128, 0, 30.0), (8, 1, 64, 33, 0.0)])
+def test_attention_packed(dtype, n_q, n_kv, hd, window, cap):
+    g = torch.Generator().manual_seed(hd + n_q)
+    lengths = [1, 37, 150, 64]
+    T = sum(lengths)
+    width = (n_q + 2 * n_kv) * hd
+    qkv = (torch.randn(T, width, generator=g)).to(dtype)
+    scale = 0.7 / math.sqrt(hd)
+    dq = qkv.to(DEV)
+    out = torch.empty(T, n_q * hd, dtype=dtype, device=DEV)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=DEV)
+    kernels.attention_simt(dq[:, :n_q * hd], out, cu, torch.tensor(lengths, dtype=torch.int32, device=DEV),
+                           n_kv=n_kv, group=n_q // n_kv, head_dim=hd, scale=scale, cap=cap, window=window,
+                           batch=len(lengths), max_q_len=max(lengths),
+                           k=dq[:, n_q * hd:(n_q + n_kv) * hd], v=dq[:, (n_q + n_kv) * hd:])
+    t = 0
+    for n in lengths:
+        s = qkv[t:t + n]
+        ref = _attention_oracle(s[:, :n_q * hd], s[:, n_q * hd:(n_q + n_kv) * hd], s[:, (n_q + n_kv) * hd:],
+                                n_q, n_kv, hd, scale, cap, window)
+        close(out[t:t + n], ref, dtype, scale=float(ref.abs().max()))
+        t += n
+
+
+def _paged_case(dtype, n_q, n_kv, hd, window, cap, lengths, page=64, special=None, seed=0):
+    """Decode pass: one query per sequence over a scattered, possibly ring-shaped cache."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(lengths)
+    ring = ((window + page - 1) // page * page) if window else (1 << 30)
+    scale = 1.0 / math.sqrt(hd)
+    ks = [torch.randn(n, n_kv * hd, generator=g).to(dtype) for n in lengths]
+    vs = [torch.randn(n, n_kv * hd, generator=g).to(dtype) for n in lengths]
+    qs = [torch.randn(1, n_q * hd, generator=g).to(dtype) for _ in lengths]
+    if special is not None:
+        special(qs, ks, vs)
+    pages_per = [min((n + page - 1) // page, ring // page) for n in lengths]
+    n_pages = sum(pages_per) + 2
+    perm = iter(torch.randperm(n_pages, generator=g).tolist())
+    pt = torch.zeros(B, max(pages_per), dtype=torch.int32)
+    kp = torch.full((n_pages, n_kv, page, hd), float("nan")).to(dtype)   # what is never written must never be read
+    vp = kp.clone()
+    for b, n in enumerate(lengths):
+        for j in range(pages_per[b]):
+            pt[b, j] = next(perm)
+        for p in range(max(0, n - ring), n):
+            ridx = p % ring
+            kp[int(pt[b, ridx // page]), :, ridx % page, :] = ks[b][p].view(n_kv, hd)
+            vp[int(pt[b, ridx // page]), :, ridx % page, :] = vs[b][p].view(n_kv, hd)
+    q = torch.cat(qs).to(DEV)
+    out = torch.empty(B, n_q * hd, dtype=dtype, device=DEV)
+    cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    kernels.attention_simt(q, out, cu, torch.tensor(lengths, dtype=torch.int32, device=DEV), n_kv=n_kv,
+                           group=n_q // n_kv, head_dim=hd, scale=scale, cap=cap, window=window, batch=B, max_q_len=1,
+                           k_pages=kp.to(DEV), v_pages=vp.to(DEV), page_table=pt.to(DEV), ring=ring, page_size=page)
+    assert bool(torch.isfinite(out.float()).all()), "a place of the cache that was never written was read"
+    for b, n in enumerate(lengths):
+        # oracle over the whole sequence with the query as the last row
+        qfull = torch.zeros(n, n_q * hd).to(dtype)
+        qfull[-1] = qs[b][0]
+        ref = _attention_oracle(qfull, ks[b], vs[b], n_q, n_kv, hd, scale, cap, window)[-1]
+        close(out[b], ref, dtype, scale=float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_q,n_kv,hd,window,cap", [(4, 2, 16, 8, 50.0), (6, 1, 32, 100, 20.0), (3, 3, 48, 0, 0.0),
+                                                    (8, 4, 256, 0, 50.0), (8, 4, 256, 70, 50.0)])
+def test_attention_paged(dtype, n_q, n_kv, hd, window, cap):
+    _paged_case(dtype, n_q, n_kv, hd, window, cap, lengths=[1, 63, 64, 65, 129, 300], seed=hd + window)
+
+
+def test_attention_far_key_stands_out():
+    """One key hundreds of places back carries almost all the weight: a kernel
+    that drops or misplaces a far page cannot pass."""
+    n_q, n_kv, hd = 4, 2, 32
+    far = 17
+
+    def special(qs, ks, vs):
+        for b in range(len(qs)):
+            if ks[b].shape[0] <= far:
+                continue
+            ks[b][far] = 0
+            qs[b][:] = 0
+            for g in range(n_kv):
+                ks[b][far, g * hd] = 8.0
+            for h in range(n_q):
+                qs[b][0, h * hd] = 8.0
+            vs[b][far] = 5.0
+
+    _paged_case(torch.float32, n_q, n_kv, hd, 0, 0.0, lengths=[400, 700, 18], special=special, seed=3)
+
+
+def test_attention_window_edge():
+    """The key exactly `window` places back must be invisible, the one after it visible."""
+    n_q, n_kv, hd, window = 2, 1, 16, 70
+
+    def special(qs, ks, vs):
+        for b in range(len(qs)):
+            n = ks[b].shape[0]
+            if n <= window:
+                continue
+            qs[b][:] = 0
+            qs[b][0, 0] = 8.0
+            qs[b][0, hd] = 8.0
+            ks[b][n - 1 - window] = 0
+            ks[b][n - 1 - window, 0] = 40.0      # just outside: would take all the weight if seen
+            vs[b][n - 1 - window] = 1000.0
+            ks[b][n - window] = 0
+            ks[b][n - window, 0] = 6.0           # just inside
+            vs[b][n - window] = 3.0
+
+    _paged_case(torch.float32, n_q, n_kv, hd, window, 0.0, lengths=[71, 128, 129, 500], special=special, seed=4)
+
+
+def test_attention_prompt_and_decode_agree_bitwise():
+    """The float path gives the same bits for a query whether it runs in a prompt or as a decode step."""
+    n_q, n_kv, hd, window, page = 4, 2, 32, 40, 64
+    g = torch.Generator().manual_seed(9)
+    n = 150
+    qkv = torch.randn(n, (n_q + 2 * n_kv) * hd, generator=g).to(DEV)
+    out = torch.empty(n, n_q * hd, device=DEV)
+    cu = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    kw = dict(n_kv=n_kv, group=2, head_dim=hd, scale=0.2, cap=30.0, window=window)
+    kernels.attention_simt(qkv[:, :n_q * hd], out, cu, torch.tensor([n], dtype=torch.int32, device=DEV), batch=1,
+                           max_q_len=n, k=qkv[:, n_q * hd:(n_q + n_kv) * hd], v=qkv[:, (n_q + n_kv) * hd:], **kw)
+    ring = 64
+    kp = torch.zeros(1, n_kv, page, hd, device=DEV)
+    vp = torch.zeros_like(kp)
+    for p in range(n - ring, n):
+        kp[0, :, p % ring, :] = qkv[p, n_q * hd:(n_q + n_kv) * hd].view(n_kv, hd)
+        vp[0, :, p % ring, :] = qkv[p, (n_q + n_kv) * hd:].view(n_kv, hd)
+    one = torch.empty(1, n_q * hd, device=DEV)
+    kernels.attention_simt(qkv[n - 1:n, :n_q * hd].contiguous(), one, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+                           torch.tensor([n], dtype=torch.int32, device=DEV), batch=1, max_q_len=1, k_pages=kp,
+                           v_pages=vp, page_table=torch.zeros(1, 1, dtype=torch.int32, device=DEV), ring=ring,
+                           page_size=page, **kw)
+    assert torch.equal(one[0], out[n - 1])
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    q = torch.zeros(2, 24, device=DEV)
+    with pytest.raises(kernels.KernelError):
+        kernels.attention_simt(q, torch.empty_like(q), torch.tensor([0, 2], dtype=torch.int32, device=DEV),
+                               torch.tensor([2], dtype=torch.int32, device=DEV), n_kv=1, group=2, head_dim=12,
+                               scale=1.0, cap=0.0, window=0, batch=1, max_q_len=2, k=q, v=q)
+    with pytest.raises(kernels.KernelError):
+        kernels.gated_act(torch.zeros(1, 8, device=DEV), torch.zeros(1, 4, device=DEV), "relu")
+    with pytest.raises(kernels.KernelError):
+        kernels.embed_scale(torch.zeros(1, dtype=torch.int32), torch.zeros(4, 4), 1.0, torch.zeros(1, 4))
