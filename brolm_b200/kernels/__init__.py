@@ -48,8 +48,18 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many of this library's own kernels have been launched by this process."""
+    return _launches
+
+
 def _check(status: int, what: str) -> None:
+    global _launches
     if status == 0:
+        _launches += 1
         return
     if status in _ERRORS:
         raise KernelError(f"{what}: {_ERRORS[status]}")
@@ -220,5 +230,5 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
              _ptr(streams), counter, _ptr(out), _stream()), "sample")
 
 
-__all__ = ["KernelBuildError", "KernelError", "build_all", "embed_scale", "rmsnorm", "residual_rmsnorm",
+__all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "embed_scale", "rmsnorm", "residual_rmsnorm",
            "rope_kv_write", "gated_act", "softcap", "linear_f32", "attention_simt", "argmax", "sample"]

@@ -13,11 +13,13 @@ from tests.plain import gemma2_plain as plain
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
-# Largest absolute error of a logit against the float64 oracle.  float32: the
-# bar wlejon/brolm sets for its own float path (tests/test_gemma2.cpp:247-248).
-# bfloat16: activations and weights carry 8 bits; the tiny models' logits are
-# of order 1 and the measured error is a few 1e-3.
-TOL = {"float32": 1e-4, "bfloat16": 3e-2}
+# Largest error of a logit against the float64 oracle, relative to the largest
+# logit of the compared rows.  Measured on whole requests of up to 300 tokens:
+# float32 5e-7 and 7e-7 for the two tiny models, bfloat16 6e-3 and 8e-3 (8-bit
+# mantissas in weights, activations and cache).  wlejon/brolm's own bars are
+# 1e-4 absolute for its float path and 5e-2 for 16 bits
+# (tests/test_gemma2.cpp:247-248).
+TOL = {"float32": 1e-5, "bfloat16": 2e-2}
 STORE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 CASES = [(name, dtype) for name in ("A", "B") for dtype in ("float32", "bfloat16")]
@@ -36,8 +38,9 @@ def setups(tmp_path_factory):
 
 
 def check(got, ref, dtype, what):
-    err = float((got.double().cpu() - ref).abs().max())
-    assert err <= TOL[dtype], f"{what}: error {err:.3e} exceeds {TOL[dtype]:.0e}"
+    ref = ref.double()
+    err = float((got.double().cpu() - ref).abs().max()) / max(float(ref.abs().max()), 1e-3)
+    assert err <= TOL[dtype], f"{what}: relative error {err:.3e} exceeds {TOL[dtype]:.0e}"
     return err
 
 
@@ -140,7 +143,7 @@ def test_padding_changes_nothing(setups, name, dtype):
     if dtype == "float32":
         assert torch.equal(alone, together[:70])
     else:
-        assert float((alone - together[:70]).abs().max()) <= TOL[dtype]
+        assert float((alone - together[:70]).abs().max()) <= TOL[dtype] * float(alone.abs().max())
 
 
 @pytest.mark.parametrize("name,dtype", CASES)
@@ -161,7 +164,7 @@ def test_greedy_generation_through_the_entry_point(setups, name, dtype):
             ids = list(p)
             for tok in o:
                 row = plain.forward(config, weights, ids)[-1]
-                assert float(row.max() - row[tok]) <= 2 * TOL[dtype]
+                assert float(row.max() - row[tok]) <= 2 * TOL[dtype] * float(row.abs().max())
                 ids.append(tok)
 
 

@@ -46,8 +46,11 @@ def test_trace_three_ways(tmp_path, name, dtype):
              for i, p in enumerate(reqs)]
     out = str(tmp_path / "whole")
     run_trace(folder, dtype, out, 192, steps)          # room for the longest request only: slots are reused
+    def near(got, ref):
+        return float((got.double() - ref).abs().max()) <= tol * float(ref.abs().max())
+
     for i, r in enumerate(refs):
-        assert float((read(out, i, V).double() - r).abs().max()) <= tol
+        assert near(read(out, i, V), r)
 
     # (2) the last 32 tokens one by one
     steps, expect, n = [], {}, 0
@@ -64,7 +67,7 @@ def test_trace_three_ways(tmp_path, name, dtype):
     out = str(tmp_path / "tail")
     run_trace(folder, dtype, out, 192, steps)
     for s, r in expect.items():
-        assert float((read(out, s, V).double() - r).abs().max()) <= tol
+        assert near(read(out, s, V), r)
 
     # (3) one batch of unequal lengths; shorter requests end earlier; then a second batch on the same cache
     def batch_steps(ids, first_step):
@@ -94,4 +97,4 @@ def test_trace_three_ways(tmp_path, name, dtype):
     out = str(tmp_path / "batched")
     run_trace(folder, dtype, out, 64 + 128 + 64 + 192, s1 + s2)
     for s, r in {**e1, **e2}.items():
-        assert float((read(out, s, V).double() - r).abs().max()) <= tol
+        assert near(read(out, s, V), r)
