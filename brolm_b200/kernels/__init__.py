@@ -212,6 +212,60 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_le
              head_dim, scale, cap, window, batch, max_q_len, _stream()), "attention_simt")
 
 
+def attention_prefill_mma(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
+                          n_kv: int, group: int, head_dim: int, scale: float, cap: float, window: int, batch: int,
+                          max_q_len: int) -> None:
+    """Tensor-core attention of whole prompts that start at position 0 (bfloat16, head_dim <= 256)."""
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
+    assert q.stride(-1) == 1 and out.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
+    assert k.stride(0) == v.stride(0) and cu_q.dtype == torch.int32
+    f = _fn("attn_mma", "brolm_attn_prefill_mma", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                                   c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int,
+                                                   c_void_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cu_q), _ptr(k), _ptr(v), k.stride(0), n_kv, group,
+             head_dim, scale, cap, window, batch, max_q_len, _stream()), "attention_prefill_mma")
+
+
+def decode_splits(batch: int, n_kv: int, max_kv_len: int, window: int, sms: int = 148) -> int:
+    """How many blocks share the keys of one (sequence, kv head): about two
+    waves of blocks over the SMs, at least two pages per block."""
+    keys = min(max_kv_len, window + 63) if window > 0 else max_kv_len
+    tiles = max(1, (keys + 63) // 64)
+    want = max(1, (2 * sms) // max(1, batch * n_kv))
+    return max(1, min(want, (tiles + 1) // 2))
+
+
+def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
+                         k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor, *, ring: int,
+                         page_size: int, n_kv: int, group: int, head_dim: int, scale: float, cap: float, window: int,
+                         batch: int, n_splits: int, scratch: Optional[tuple] = None) -> None:
+    """Tensor-core attention of one new token per sequence over the paged cache
+    (bfloat16, head_dim <= 256, group <= 16, pages of 64 keys).  With more than
+    one split the partial results go through float32 scratch: ``scratch`` =
+    (part_o [batch * n_q * n_splits * head_dim], part_ml [batch * n_q * n_splits * 2]),
+    made here when it is not given."""
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16
+    assert q.stride(-1) == 1 and out.stride(-1) == 1 and k_pages.is_contiguous() and v_pages.is_contiguous()
+    assert tuple(k_pages.shape[1:]) == (n_kv, page_size, head_dim)
+    assert page_table.dtype == torch.int32 and page_table.stride(1) == 1
+    assert cu_q.dtype == torch.int32 and kv_len.dtype == torch.int32
+    part_o = part_ml = None
+    if n_splits > 1:
+        n = batch * n_kv * group * n_splits
+        if scratch is None:
+            part_o = torch.empty(n * head_dim, dtype=torch.float32, device=q.device)
+            part_ml = torch.empty(n * 2, dtype=torch.float32, device=q.device)
+        else:
+            part_o, part_ml = scratch
+            assert part_o.numel() >= n * head_dim and part_ml.numel() >= n * 2
+    f = _fn("attn_mma", "brolm_attn_decode_mma", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                  c_float, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cu_q), _ptr(kv_len), _ptr(k_pages), _ptr(v_pages),
+             _ptr(page_table), page_table.stride(0), ring, page_size, n_kv, group, head_dim, scale, cap, window,
+             batch, n_splits, _ptr(part_o), _ptr(part_ml), _stream()), "attention_decode_mma")
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     """out[r] (int32) = first index of the maximum of logits[r] (float32)."""
     assert logits.dtype == torch.float32 and logits.is_contiguous() and out.dtype == torch.int32
@@ -231,4 +285,5 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
 
 
 __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "embed_scale", "rmsnorm", "residual_rmsnorm",
-           "rope_kv_write", "gated_act", "softcap", "linear_f32", "attention_simt", "argmax", "sample"]
+           "rope_kv_write", "gated_act", "softcap", "linear_f32", "attention_simt", "attention_prefill_mma", "attention_decode_mma",
+           "decode_splits", "argmax", "sample"]

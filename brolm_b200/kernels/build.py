@@ -33,6 +33,7 @@ LIBRARIES: dict[str, list[str]] = {
     "core": ["core.cu"],
     "linear_f32": ["linear_f32.cu"],
     "attn_simt": ["attn_simt.cu"],
+    "attn_mma": ["attn_mma.cu"],
     "sampling": ["sampling.cu"],
 }
 HEADERS = ["common.cuh"]

@@ -82,13 +82,26 @@ class Attention(Part):
             self.attend_paged(q, out, ctx, common, k_pages, v_pages, table, ring, page)
         return linear(out, self.w_o, out_dtype=torch.float32)
 
-    # the two attention calls are methods so that a faster kernel can take them over
+    # bfloat16 runs on the tensor cores when the sizes allow; everything else, and
+    # all of float32, takes the exact CUDA-core kernel
+    def _tensor_cores(self, ctx) -> bool:
+        return ctx.dtype == torch.bfloat16 and self.head_dim <= 256 and self.n_q // self.n_kv <= 16
+
     def attend_packed(self, q, k, v, out, ctx, common):
-        kernels.attention_simt(q, out, ctx.cu_q, ctx.kv_len, k=k, v=v, **common)
+        if self._tensor_cores(ctx):
+            kernels.attention_prefill_mma(q, out, ctx.cu_q, k, v, **common)
+        else:
+            kernels.attention_simt(q, out, ctx.cu_q, ctx.kv_len, k=k, v=v, **common)
 
     def attend_paged(self, q, out, ctx, common, k_pages, v_pages, table, ring, page):
-        kernels.attention_simt(q, out, ctx.cu_q, ctx.kv_len, k_pages=k_pages, v_pages=v_pages, page_table=table,
-                               ring=ring, page_size=page, **common)
+        if self._tensor_cores(ctx) and ctx.mode == "decode" and page == 64:
+            args = {k: v for k, v in common.items() if k != "max_q_len"}
+            splits = kernels.decode_splits(ctx.batch, self.n_kv, max(ctx.host_lengths), self.window or 0)
+            kernels.attention_decode_mma(q, out, ctx.cu_q, ctx.kv_len, k_pages, v_pages, table, ring=ring,
+                                         page_size=page, n_splits=splits, **args)
+        else:
+            kernels.attention_simt(q, out, ctx.cu_q, ctx.kv_len, k_pages=k_pages, v_pages=v_pages, page_table=table,
+                                   ring=ring, page_size=page, **common)
 
 
 register_part("mixer", "attention", Attention)

@@ -193,12 +193,13 @@ def _attention_oracle(q, k, v, n_q, n_kv, hd, scale, cap, window):
     return plain.attention(q, k, v, n_q, n_kv, hd, scale, cap, window)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "simt"), (torch.bfloat16, "simt"), (torch.bfloat16, "mma")])
 @pytest.mark.parametrize("n_q,n_kv,hd,window,cap", [(4, 2, 16, 8, 50.0), (6, 1, 32, 16, 20.0), (3, 3, 48, 0, 0.0),
-                                                    (8, 4, 256, 100, 50.0), (5, 5, 128, 0, 30.0), (8, 1, 64, 33, 0.0)])
-def test_attention_packed(dtype, n_q, n_kv, hd, window, cap):
+                                                    (8, 4, 256, 100, 50.0), (5, 5, 128, 0, 30.0), (8, 1, 64, 33, 0.0),
+                                                    (16, 1, 80, 70, 10.0)])
+def test_attention_packed(dtype, kernel, n_q, n_kv, hd, window, cap):
     g = torch.Generator().manual_seed(hd + n_q)
-    lengths = [1, 37, 150, 64]
+    lengths = [1, 37, 150, 64, 300]
     T = sum(lengths)
     width = (n_q + 2 * n_kv) * hd
     qkv = (torch.randn(T, width, generator=g)).to(dtype)
@@ -206,10 +207,14 @@ def test_attention_packed(dtype, n_q, n_kv, hd, window, cap):
     dq = qkv.to(DEV)
     out = torch.empty(T, n_q * hd, dtype=dtype, device=DEV)
     cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=DEV)
-    kernels.attention_simt(dq[:, :n_q * hd], out, cu, torch.tensor(lengths, dtype=torch.int32, device=DEV),
-                           n_kv=n_kv, group=n_q // n_kv, head_dim=hd, scale=scale, cap=cap, window=window,
-                           batch=len(lengths), max_q_len=max(lengths),
-                           k=dq[:, n_q * hd:(n_q + n_kv) * hd], v=dq[:, (n_q + n_kv) * hd:])
+    kw = dict(n_kv=n_kv, group=n_q // n_kv, head_dim=hd, scale=scale, cap=cap, window=window,
+              batch=len(lengths), max_q_len=max(lengths))
+    kk, vv = dq[:, n_q * hd:(n_q + n_kv) * hd], dq[:, (n_q + n_kv) * hd:]
+    if kernel == "mma":
+        kernels.attention_prefill_mma(dq[:, :n_q * hd], out, cu, kk, vv, **kw)
+    else:
+        kernels.attention_simt(dq[:, :n_q * hd], out, cu, torch.tensor(lengths, dtype=torch.int32, device=DEV),
+                               k=kk, v=vv, **kw)
     t = 0
     for n in lengths:
         s = qkv[t:t + n]
@@ -219,7 +224,7 @@ def test_attention_packed(dtype, n_q, n_kv, hd, window, cap):
         t += n
 
 
-def _paged_case(dtype, n_q, n_kv, hd, window, cap, lengths, page=64, special=None, seed=0):
+def _paged_case(dtype, n_q, n_kv, hd, window, cap, lengths, page=64, special=None, seed=0, kernel="simt", splits=1):
     """Decode pass: one query per sequence over a scattered, possibly ring-shaped cache."""
     g = torch.Generator().manual_seed(seed)
     B = len(lengths)
@@ -246,9 +251,14 @@ def _paged_case(dtype, n_q, n_kv, hd, window, cap, lengths, page=64, special=Non
     q = torch.cat(qs).to(DEV)
     out = torch.empty(B, n_q * hd, dtype=dtype, device=DEV)
     cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
-    kernels.attention_simt(q, out, cu, torch.tensor(lengths, dtype=torch.int32, device=DEV), n_kv=n_kv,
-                           group=n_q // n_kv, head_dim=hd, scale=scale, cap=cap, window=window, batch=B, max_q_len=1,
-                           k_pages=kp.to(DEV), v_pages=vp.to(DEV), page_table=pt.to(DEV), ring=ring, page_size=page)
+    kvl = torch.tensor(lengths, dtype=torch.int32, device=DEV)
+    kw = dict(n_kv=n_kv, group=n_q // n_kv, head_dim=hd, scale=scale, cap=cap, window=window, batch=B)
+    if kernel == "mma":
+        kernels.attention_decode_mma(q, out, cu, kvl, kp.to(DEV), vp.to(DEV), pt.to(DEV), ring=ring, page_size=page,
+                                     n_splits=splits, **kw)
+    else:
+        kernels.attention_simt(q, out, cu, kvl, max_q_len=1, k_pages=kp.to(DEV), v_pages=vp.to(DEV),
+                               page_table=pt.to(DEV), ring=ring, page_size=page, **kw)
     assert bool(torch.isfinite(out.float()).all()), "a place of the cache that was never written was read"
     for b, n in enumerate(lengths):
         # oracle over the whole sequence with the query as the last row
@@ -265,7 +275,33 @@ def test_attention_paged(dtype, n_q, n_kv, hd, window, cap):
     _paged_case(dtype, n_q, n_kv, hd, window, cap, lengths=[1, 63, 64, 65, 129, 300], seed=hd + window)
 
 
-def test_attention_far_key_stands_out():
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+@pytest.mark.parametrize("n_q,n_kv,hd,window,cap", [(4, 2, 16, 8, 50.0), (6, 1, 32, 100, 20.0), (3, 3, 48, 0, 0.0),
+                                                    (8, 4, 256, 0, 50.0), (8, 4, 256, 70, 50.0), (16, 1, 128, 0, 0.0),
+                                                    (5, 1, 80, 200, 30.0)])
+def test_attention_decode_tensor_cores(splits, n_q, n_kv, hd, window, cap):
+    _paged_case(torch.bfloat16, n_q, n_kv, hd, window, cap, lengths=[1, 63, 64, 65, 129, 300, 1000],
+                seed=hd + window, kernel="mma", splits=splits)
+
+
+def test_attention_decode_tensor_cores_skips_padding_rows():
+    """A row with kv_len 0 is padding: its output is zero and the cache is not read for it."""
+    n_q, n_kv, hd = 4, 2, 64
+    kp = torch.randn(3, n_kv, 64, hd).to(torch.bfloat16).to(DEV)
+    q = torch.randn(3, n_q * hd).to(torch.bfloat16).to(DEV)
+    out = torch.full((3, n_q * hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    pt = torch.tensor([[0, 1], [0, 0], [2, 0]], dtype=torch.int32, device=DEV)
+    for splits in (1, 3):
+        kernels.attention_decode_mma(q, out, torch.arange(4, dtype=torch.int32, device=DEV),
+                                     torch.tensor([100, 0, 5], dtype=torch.int32, device=DEV), kp, kp, pt,
+                                     ring=1 << 30, page_size=64, n_kv=n_kv, group=2, head_dim=hd, scale=0.1, cap=0.0,
+                                     window=0, batch=3, n_splits=splits)
+        assert float(out[1].float().abs().max()) == 0.0 and float(out[0].float().abs().max()) > 0
+
+
+@pytest.mark.parametrize("dtype,kernel,splits", [(torch.float32, "simt", 1), (torch.bfloat16, "mma", 1),
+                                                 (torch.bfloat16, "mma", 4)])
+def test_attention_far_key_stands_out(dtype, kernel, splits):
     """One key hundreds of places back carries almost all the weight: a kernel
     that drops or misplaces a far page cannot pass."""
     n_q, n_kv, hd = 4, 2, 32
@@ -283,10 +319,13 @@ def test_attention_far_key_stands_out():
                 qs[b][0, h * hd] = 8.0
             vs[b][far] = 5.0
 
-    _paged_case(torch.float32, n_q, n_kv, hd, 0, 0.0, lengths=[400, 700, 18], special=special, seed=3)
+    _paged_case(dtype, n_q, n_kv, hd, 0, 0.0, lengths=[400, 700, 18], special=special, seed=3, kernel=kernel,
+                splits=splits)
 
 
-def test_attention_window_edge():
+@pytest.mark.parametrize("dtype,kernel,splits", [(torch.float32, "simt", 1), (torch.bfloat16, "mma", 1),
+                                                 (torch.bfloat16, "mma", 3)])
+def test_attention_window_edge(dtype, kernel, splits):
     """The key exactly `window` places back must be invisible, the one after it visible."""
     n_q, n_kv, hd, window = 2, 1, 16, 70
 
@@ -305,7 +344,8 @@ def test_attention_window_edge():
             ks[b][n - window, 0] = 6.0           # just inside
             vs[b][n - window] = 3.0
 
-    _paged_case(torch.float32, n_q, n_kv, hd, window, 0.0, lengths=[71, 128, 129, 500], special=special, seed=4)
+    _paged_case(dtype, n_q, n_kv, hd, window, 0.0, lengths=[71, 128, 129, 500], special=special, seed=4,
+                kernel=kernel, splits=splits)
 
 
 def test_attention_prompt_and_decode_agree_bitwise():
