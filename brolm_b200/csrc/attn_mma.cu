@@ -115,11 +115,13 @@ __device__ __forceinline__ float score_of(float s, float scale, float cap, float
 // ===========================================================================
 // prompts
 // ===========================================================================
-template <int HD_MAX>
+// EXACT: head_dim == HD_MAX, known to the compiler (all index arithmetic folds).
+template <int HD_MAX, bool EXACT>
 __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int hd = a.hd, hd16 = hd >> 4, cpr = hd >> 3;
+    const int hd = EXACT ? HD_MAX : a.hd, hd16 = hd >> 4, cpr = hd >> 3;
     const bool swz = (hd & 63) == 0;
+    const uint32_t rowb = (uint32_t)hd * 2u;
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
     bf16* Ks = Qs + BM * hd;
     bf16* Vs = Ks + KT * hd;
@@ -172,6 +174,18 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
     }
     const float inv_cap = a.cap > 0.0f ? 1.0f / a.cap : 0.0f;
 
+    // Per-thread ldmatrix addresses.  The chunk (2 ks + j) of a row r lives at
+    // ((32 ks) ^ xhi) + lo with xhi = ((r & 7) & 6) << 4 and lo = (j ^ (r & 1)) << 4
+    // when the tile is swizzled (xhi = 0, lo = j << 4 when it is not); r & 7 is
+    // lane & 7 for every row a thread addresses.
+    const uint32_t x = lane & 7;
+    const uint32_t xhi = swz ? (x & 6u) << 4 : 0u;
+    const uint32_t jq = lane >> 4, jk = (lane >> 3) & 1, jv = lane >> 4;
+    const uint32_t q_addr = qs_base + (warp * 16 + (lane & 15)) * rowb + ((swz ? (jq ^ (x & 1u)) : jq) << 4);
+    const uint32_t k_addr = ks_base + ((lane & 7) + ((lane >> 4) << 3)) * rowb + ((swz ? (jk ^ (x & 1u)) : jk) << 4);
+    const uint32_t v_addr = vs_base + ((lane & 7) + (((lane >> 3) & 1) << 3)) * rowb + ((swz ? (jv ^ (x & 1u)) : jv) << 4);
+    const uint32_t kt_stride = 16u * rowb;
+
     for (int t = t_first; t <= t_last; ++t) {
         load_kv(a.v, vs_base, t);
         cp_async_commit();
@@ -185,13 +199,12 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
         for (int ks = 0; ks < HD_MAX / 16; ++ks) {
             if (ks < hd16) {
                 uint32_t af[4];
-                ldmatrix_x4(qs_base + tile_off(warp * 16 + (lane & 15), ks * 2 + (lane >> 4), hd, swz), af[0], af[1],
-                            af[2], af[3]);
+                const uint32_t coff = ((uint32_t)ks << 5) ^ xhi;
+                ldmatrix_x4(q_addr + coff, af[0], af[1], af[2], af[3]);
 #pragma unroll
                 for (int kt = 0; kt < 4; ++kt) {
                     uint32_t b0, b1, b2, b3;
-                    ldmatrix_x4(ks_base + tile_off(kt * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1),
-                                                   hd, swz), b0, b1, b2, b3);
+                    ldmatrix_x4(k_addr + kt * kt_stride + coff, b0, b1, b2, b3);
                     mma_bf16(s[2 * kt], af, b0, b1);
                     mma_bf16(s[2 * kt + 1], af, b2, b3);
                 }
@@ -258,8 +271,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
             for (int dp = 0; dp < HD_MAX / 16; ++dp) {
                 if (dp < hd16) {
                     uint32_t b0, b1, b2, b3;
-                    ldmatrix_x4_trans(vs_base + tile_off(kt * 16 + (lane & 7) + (((lane >> 3) & 1) << 3),
-                                                         dp * 2 + (lane >> 4), hd, swz), b0, b1, b2, b3);
+                    ldmatrix_x4_trans(v_addr + kt * kt_stride + (((uint32_t)dp << 5) ^ xhi), b0, b1, b2, b3);
                     mma_bf16(o[2 * dp], pf[kt], b0, b1);
                     mma_bf16(o[2 * dp + 1], pf[kt], b2, b3);
                 }
@@ -292,11 +304,12 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
 // ===========================================================================
 constexpr int STAGES = 3;
 
-template <int HD_MAX>
+template <int HD_MAX, bool EXACT>
 __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int hd = a.hd, hd16 = hd >> 4, cpr = hd >> 3;
+    const int hd = EXACT ? HD_MAX : a.hd, hd16 = hd >> 4, cpr = hd >> 3;
     const bool swz = (hd & 63) == 0;
+    const uint32_t rowb = (uint32_t)hd * 2u;
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);            // [16][hd]
     bf16* stage0 = Qs + 16 * hd;                             // STAGES x ([KT][hd] keys, [KT][hd] values)
     const uint32_t qs_base = smem_u32(Qs), st_base = smem_u32(stage0);
@@ -325,10 +338,12 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
         cp_async16(qs_base + tile_off(r, c, hd, swz),
                    a.q + (size_t)a.cu_q[b] * a.q_stride + (g * a.group + (ok ? r : 0)) * hd + c * 8, ok ? 16 : 0);
     }
-    auto load_tile = [&](int i) {                             // i-th tile of the split into stage i % STAGES
+    auto page_of = [&](int i) -> int {                        // page that holds the i-th tile of the split
+        const int ridx = (int)(((long long)(t_begin + i) * KT) % a.ring);
+        return a.page_table[(size_t)b * a.pt_stride + ridx / KT];
+    };
+    auto load_tile = [&](int i, int page) {                   // i-th tile of the split into stage i % STAGES
         const int t = t_begin + i;
-        const int ridx = (int)(((long long)t * KT) % a.ring);
-        const int page = a.page_table[(size_t)b * a.pt_stride + ridx / KT];
         const size_t src = ((size_t)page * a.n_kv + g) * KT * hd;
         const uint32_t kb = st_base + (i % STAGES) * stage_bytes, vb = kb + KT * hd * 2u;
         for (int idx = threadIdx.x; idx < KT * cpr; idx += NTHREADS) {
@@ -342,9 +357,19 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
     };
 #pragma unroll
     for (int i = 0; i < STAGES - 1; ++i) {
-        if (i < n_tiles) load_tile(i);
+        if (i < n_tiles) load_tile(i, page_of(i));
         cp_async_commit();
     }
+    // the page id of the tile that the next iteration will load is fetched one iteration early
+    int page_next = (STAGES - 1 < n_tiles) ? page_of(STAGES - 1) : 0;
+
+    const uint32_t x = lane & 7;
+    const uint32_t xhi = swz ? (x & 6u) << 4 : 0u;
+    const uint32_t jq = lane >> 4, jk = (lane >> 3) & 1, jv = lane >> 4;
+    const uint32_t q_addr = qs_base + (lane & 15) * rowb + ((swz ? (jq ^ (x & 1u)) : jq) << 4);
+    const uint32_t k_thr = (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * rowb + ((swz ? (jk ^ (x & 1u)) : jk) << 4);
+    const uint32_t v_thr = KT * rowb + (warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * rowb +
+                           ((swz ? (jv ^ (x & 1u)) : jv) << 4);
 
     float o[HD_MAX / 8][4];
 #pragma unroll
@@ -355,9 +380,10 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
     for (int i = 0; i < n_tiles; ++i) {
         cp_async_wait<STAGES - 2>();
         __syncthreads();                       // tile i has landed; everyone is done with tile i - 1
-        if (i + STAGES - 1 < n_tiles) load_tile(i + STAGES - 1);
+        if (i + STAGES - 1 < n_tiles) load_tile(i + STAGES - 1, page_next);
         cp_async_commit();
-        const uint32_t kb = st_base + (i % STAGES) * stage_bytes, vb = kb + KT * hd * 2u;
+        if (i + STAGES < n_tiles) page_next = page_of(i + STAGES);
+        const uint32_t sb = st_base + (i % STAGES) * stage_bytes;
         const int t = t_begin + i;
 
         float s[2][4];
@@ -367,9 +393,9 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
         for (int ks = 0; ks < HD_MAX / 16; ++ks) {
             if (ks < hd16) {
                 uint32_t af[4], b0, b1, b2, b3;
-                ldmatrix_x4(qs_base + tile_off(lane & 15, ks * 2 + (lane >> 4), hd, swz), af[0], af[1], af[2], af[3]);
-                ldmatrix_x4(kb + tile_off(warp * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1), hd, swz),
-                            b0, b1, b2, b3);
+                const uint32_t coff = ((uint32_t)ks << 5) ^ xhi;
+                ldmatrix_x4(q_addr + coff, af[0], af[1], af[2], af[3]);
+                ldmatrix_x4(sb + k_thr + coff, b0, b1, b2, b3);
                 mma_bf16(s[0], af, b0, b1);
                 mma_bf16(s[1], af, b2, b3);
             }
@@ -417,8 +443,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
         for (int dp = 0; dp < HD_MAX / 16; ++dp) {
             if (dp < hd16) {
                 uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(vb + tile_off(warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), dp * 2 + (lane >> 4),
-                                                hd, swz), b0, b1, b2, b3);
+                ldmatrix_x4_trans(sb + v_thr + (((uint32_t)dp << 5) ^ xhi), b0, b1, b2, b3);
                 mma_bf16(o[2 * dp], pf, b0, b1);
                 mma_bf16(o[2 * dp + 1], pf, b2, b3);
             }
@@ -503,25 +528,33 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
     }
 }
 
-template <int HD_MAX>
+template <int HD_MAX, bool EXACT>
 int launch_prefill(const MmaArgs& a, int batch, int max_q_len, cudaStream_t stream) {
     const size_t smem = (size_t)(BM + 2 * KT) * a.hd * sizeof(bf16);
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD_MAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    static size_t allowed = 0;               // raised once per size, not at every launch
+    if (smem > allowed) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD_MAX, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        allowed = smem;
+    }
     dim3 grid((max_q_len * a.group + BM - 1) / BM, a.n_kv, batch);
-    attn_prefill_mma_kernel<HD_MAX><<<grid, NTHREADS, smem, stream>>>(a);
+    attn_prefill_mma_kernel<HD_MAX, EXACT><<<grid, NTHREADS, smem, stream>>>(a);
     return launch_status();
 }
 
-template <int HD_MAX>
+template <int HD_MAX, bool EXACT>
 int launch_decode(const MmaArgs& a, int batch, cudaStream_t stream) {
     size_t smem = (size_t)(16 + STAGES * 2 * KT) * a.hd * sizeof(bf16);
     const size_t merge = (size_t)(8 * 16 + 4 * a.group * a.hd) * sizeof(float) + 16 * a.hd * sizeof(bf16);
     if (merge > smem) smem = merge;
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD_MAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    static size_t allowed = 0;
+    if (smem > allowed) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD_MAX, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        allowed = smem;
+    }
     dim3 grid(a.n_splits, a.n_kv, batch);
-    attn_decode_mma_kernel<HD_MAX><<<grid, NTHREADS, smem, stream>>>(a);
+    attn_decode_mma_kernel<HD_MAX, EXACT><<<grid, NTHREADS, smem, stream>>>(a);
     int st = launch_status();
     if (st != 0 || a.n_splits == 1) return st;
     dim3 cgrid(a.n_kv * a.group, batch);
@@ -554,9 +587,12 @@ BROLM_API int brolm_attn_prefill_mma(const void* q, int q_stride, void* out, int
     a.q = (const bf16*)q; a.out = (bf16*)out; a.q_stride = q_stride; a.out_stride = out_stride;
     a.cu_q = (const int32_t*)cu_q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.kv_stride = kv_stride;
     a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window; a.n_splits = 1;
-    if (hd <= 64) return launch_prefill<64>(a, batch, max_q_len, stream);
-    if (hd <= 128) return launch_prefill<128>(a, batch, max_q_len, stream);
-    return launch_prefill<256>(a, batch, max_q_len, stream);
+    if (hd == 64) return launch_prefill<64, true>(a, batch, max_q_len, stream);
+    if (hd == 128) return launch_prefill<128, true>(a, batch, max_q_len, stream);
+    if (hd == 256) return launch_prefill<256, true>(a, batch, max_q_len, stream);
+    if (hd < 64) return launch_prefill<64, false>(a, batch, max_q_len, stream);
+    if (hd < 128) return launch_prefill<128, false>(a, batch, max_q_len, stream);
+    return launch_prefill<256, false>(a, batch, max_q_len, stream);
 }
 
 // One query token per sequence (row cu_q[b] of q) over the paged cache.  The page size is
@@ -581,7 +617,10 @@ BROLM_API int brolm_attn_decode_mma(const void* q, int q_stride, void* out, int 
     a.pt_stride = pt_stride; a.ring = ring;
     a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window;
     a.n_splits = n_splits; a.part_o = (float*)part_o; a.part_ml = (float*)part_ml;
-    if (hd <= 64) return launch_decode<64>(a, batch, stream);
-    if (hd <= 128) return launch_decode<128>(a, batch, stream);
-    return launch_decode<256>(a, batch, stream);
+    if (hd == 64) return launch_decode<64, true>(a, batch, stream);
+    if (hd == 128) return launch_decode<128, true>(a, batch, stream);
+    if (hd == 256) return launch_decode<256, true>(a, batch, stream);
+    if (hd < 64) return launch_decode<64, false>(a, batch, stream);
+    if (hd < 128) return launch_decode<128, false>(a, batch, stream);
+    return launch_decode<256, false>(a, batch, stream);
 }

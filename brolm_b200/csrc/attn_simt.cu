@@ -201,16 +201,19 @@ int launch(const AttnArgs& a, bool paged, int batch, int max_q_len, cudaStream_t
     const size_t smem = (size_t)((ROWS + KT) * (a.hd + 4) + KT * a.hd) * sizeof(float);
     if (smem > 227 * 1024) return BROLM_ERR_TOO_LARGE;
     dim3 grid((max_q_len * a.group + ROWS - 1) / ROWS, a.n_kv, batch);
-    cudaError_t e;
-    if (paged) {
-        e = cudaFuncSetAttribute(attn_simt_kernel<T, DPL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static size_t allowed[2] = {0, 0};        // raised once per size, not at every launch
+    if (smem > allowed[paged]) {
+        cudaError_t e = paged ? cudaFuncSetAttribute(attn_simt_kernel<T, DPL, true>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                              : cudaFuncSetAttribute(attn_simt_kernel<T, DPL, false>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        attn_simt_kernel<T, DPL, true><<<grid, WARPS * 32, smem, stream>>>(a);
-    } else {
-        e = cudaFuncSetAttribute(attn_simt_kernel<T, DPL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        attn_simt_kernel<T, DPL, false><<<grid, WARPS * 32, smem, stream>>>(a);
+        allowed[paged] = smem;
     }
+    if (paged)
+        attn_simt_kernel<T, DPL, true><<<grid, WARPS * 32, smem, stream>>>(a);
+    else
+        attn_simt_kernel<T, DPL, false><<<grid, WARPS * 32, smem, stream>>>(a);
     return launch_status();
 }
 

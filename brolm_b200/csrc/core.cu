@@ -259,11 +259,11 @@ __device__ __forceinline__ float act_apply(float z, int act) {
 
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int act) {
-    const size_t t = blockIdx.y;
+    const size_t t = blockIdx.x;
     const T* g = gate_up + t * 2 * (size_t)inter;
     const T* u = g + inter;
     T* o = out + t * (size_t)inter;
-    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < inter; j += gridDim.x * blockDim.x)
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < inter; j += gridDim.y * blockDim.x)
         o[j] = from_float<T>(act_apply(to_float(g[j]), act) * to_float(u[j]));
 }
 
@@ -271,8 +271,9 @@ BROLM_API int brolm_gated_act(const void* gate_up, void* out, int dtype, int tok
                               cudaStream_t stream) {
     if (tokens <= 0) return BROLM_OK;
     if (act < 0 || act > 1) return BROLM_ERR_BAD_SIZE;
-    if (tokens > 65535) return BROLM_ERR_TOO_LARGE;
-    dim3 grid((inter + 1023) / 1024, tokens);
+    int by = (inter + 1023) / 1024;
+    if (by > 65535) by = 65535;
+    dim3 grid(tokens, by);
     if (dtype == BROLM_F32)
         gated_act_kernel<float><<<grid, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, act);
     else if (dtype == BROLM_BF16)

@@ -33,6 +33,11 @@ class StepContext:
     max_q_len: int
     page_tables: list              # per key/value group: int32 [batch, width] on the device
     host_lengths: list             # host copy of kv_len
+    max_kv_len: int = 0            # an upper bound of kv_len for sizing launches (a captured graph fixes it)
+
+    def __post_init__(self):
+        if not self.max_kv_len:
+            self.max_kv_len = max(self.host_lengths) if self.host_lengths else 0
 
     def kv(self, entry: CacheEntry):
         """(k_pages, v_pages, page_table, ring, page_size) of a key/value entry."""

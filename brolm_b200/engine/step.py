@@ -5,11 +5,20 @@ of unequal lengths, run packed back to back) or extends each of them by one
 token.  It runs only the tokens it is given, reads what earlier steps left in
 the cache, and returns float32 logits at the wanted places.
 
+Decode steps are replayed from a captured CUDA graph: the step's tokens,
+positions, lengths and page tables live in a device buffer of fixed layout
+that one host-to-device copy refreshes, so the ~300 launches of a step cost
+one graph launch (the idea of device-resident step state is wlejon/brolm's,
+src/detail/dense_decoder.cpp:335-524, which it does not wire for Gemma 2,
+include/brolm/gemma2.h:42-43).  A batch is padded to the next power of two;
+padding rows have position -1 and length 0 and change no result.
+
 wlejon/brolm's forward/forward_last take one sequence at ``cache_len``
 (include/brolm/gemma2.h:119-129); the batched form is this framework's own.
 """
 from __future__ import annotations
 
+import dataclasses
 from typing import Optional, Sequence
 
 import numpy as np
@@ -24,15 +33,101 @@ class StepError(ValueError):
     pass
 
 
+@dataclasses.dataclass
+class _Plan:
+    mode: str
+    slots: list
+    n_new: list
+    old: list
+    new_len: list
+    flat: np.ndarray        # all tokens of the step, packed
+    rows: list              # packed row of every wanted place
+
+
+def _next_pow2(n: int) -> int:
+    return 1 << max(0, (n - 1).bit_length())
+
+
+class _DecodeGraph:
+    """One captured decode step for a padded batch size and a bound on the lengths."""
+
+    def __init__(self, engine: "Engine", rows: int, kv_cap: int):
+        cache, dev = engine.cache, engine.device
+        self.rows, self.kv_cap = rows, kv_cap
+        self.widths = []
+        for g in cache.kv_groups:
+            w = (cache.max_positions + g.page_size - 1) // g.page_size
+            if g.ring:
+                w = min(w, g.ring // g.page_size)
+            self.widths.append(max(1, w))
+        n = 4 * rows + sum(rows * w for w in self.widths)
+        self.host = torch.zeros(n, dtype=torch.int32, pin_memory=True)
+        self.hv = self.host.numpy()
+        self.dev = torch.zeros(n, dtype=torch.int32, device=dev)
+        seg = [self.dev[i * rows:(i + 1) * rows] for i in range(4)]
+        off = 4 * rows
+        tables = []
+        for w in self.widths:
+            tables.append(self.dev[off:off + rows * w].view(rows, w))
+            off += rows * w
+        self.tokens = seg[0]
+        ar = torch.arange(rows + 1, dtype=torch.int32, device=dev)
+        self.ctx = StepContext(
+            mode="decode", dtype=engine.model.dtype, device=dev, cache=cache, batch=rows, n_tokens=rows, slots=[],
+            positions=seg[1], tok_seq=ar[:rows].clone(), cu_q=ar, kv_len=seg[2], slots_dev=seg[3], max_q_len=1,
+            page_tables=tables, host_lengths=[], max_kv_len=kv_cap)
+        self.all_rows = ar[:rows].clone()
+        # an all-padding state: the warm-up pass touches no cache
+        self.hv[:] = 0
+        self.hv[rows:2 * rows] = -1
+        self.hv[3 * rows:4 * rows] = 0
+        self.dev.copy_(self.host)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            engine.model.forward(self.ctx, self.tokens, self.all_rows)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self.copied = torch.cuda.Event()
+        self.copied.record()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, pool=engine._graph_pool):
+            self.logits = engine.model.forward(self.ctx, self.tokens, self.all_rows)
+
+    def run(self, plan: _Plan, cache: Cache) -> torch.Tensor:
+        R, B = self.rows, len(plan.slots)
+        hv = self.hv
+        self.copied.synchronize()              # the copy of the step before has left the pinned buffer
+        hv[:4 * R] = 0
+        hv[R:2 * R] = -1
+        hv[0:B] = plan.flat
+        hv[R:R + B] = plan.old
+        hv[2 * R:2 * R + B] = plan.new_len
+        hv[3 * R:3 * R + B] = plan.slots
+        off = 4 * R
+        for g, w in enumerate(self.widths):
+            t = cache.page_table(g, plan.slots, width=w, rows=R)
+            hv[off:off + R * w] = t.numpy().reshape(-1)
+            off += R * w
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+        self.graph.replay()
+        return self.logits
+
+
 class Engine:
     """A model with a cache: slots, steps, and nothing else."""
 
     def __init__(self, model: DecoderModel, max_tokens: int, max_slots: Optional[int] = None,
-                 max_seq_len: Optional[int] = None):
+                 max_seq_len: Optional[int] = None, use_graphs: bool = True):
         self.model = model
         self.cache: Cache = model.new_cache(max_tokens, max_slots, max_seq_len)
         self.device = model.device
         self.vocab = model.layout.embedding.vocab
+        parts = [p for blk in model.blocks for p in blk.parts().values() if p is not None] + [model.final_norm]
+        self.use_graphs = bool(use_graphs and self.device.type == "cuda" and all(p.graph_safe for p in parts))
+        self._graphs: dict[tuple, _DecodeGraph] = {}
+        self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
 
     # slots ----------------------------------------------------------------
     def open(self, n: int = 1) -> list[int]:
@@ -51,14 +146,32 @@ class Engine:
         """Run ``tokens[i]`` on ``slots[i]``; return logits [wanted, vocab] (float32, device).
 
         ``want[i]`` lists the places among ``tokens[i]`` whose logits are
-        wanted (default: the last one of each), in the order given.
+        wanted (default: the last one of each), in the order given.  The
+        result of a decode step is valid until the next step.
         """
-        ctx, tok_dev, rows = self._prepare(slots, tokens, want)
-        logits = self.model.forward(ctx, tok_dev, rows)
-        self.cache.commit(dict(zip(slots, ctx.host_lengths)))
+        plan = self._plan(slots, tokens, want)
+        if plan.mode == "decode" and self.use_graphs:
+            logits = self._graph_for(plan).run(plan, self.cache)
+            if plan.rows != list(range(len(plan.slots))):
+                logits = logits[torch.tensor(plan.rows, dtype=torch.long, device=self.device)]
+            else:
+                logits = logits[:len(plan.slots)]
+        else:
+            ctx, tok_dev, rows = self._context(plan)
+            logits = self.model.forward(ctx, tok_dev, rows)
+        self.cache.commit(dict(zip(plan.slots, plan.new_len)))
         return logits
 
-    def _prepare(self, slots, tokens, want):
+    def _graph_for(self, plan: _Plan) -> _DecodeGraph:
+        rows = _next_pow2(len(plan.slots))
+        kv_cap = min(max(256, _next_pow2(max(plan.new_len))), _next_pow2(self.cache.max_positions))
+        key = (rows, kv_cap)
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._graphs[key] = _DecodeGraph(self, rows, kv_cap)
+        return g
+
+    def _plan(self, slots, tokens, want) -> _Plan:
         B = len(slots)
         if B == 0 or len(tokens) != B:
             raise StepError("step: needs as many token lists as slots, and at least one")
@@ -87,23 +200,27 @@ class Engine:
             want = [[n - 1] for n in n_new]
         if len(want) != B:
             raise StepError("step: 'want' needs one list per sequence")
-        cache.reserve(dict(zip(slots, new_len)))
-
-        T = int(sum(n_new))
-        cu = np.zeros(B + 1, dtype=np.int64)
-        np.cumsum(n_new, out=cu[1:])
-        rows = []
+        rows, start = [], 0
         for i, w in enumerate(want):
             for p in w:
                 if not 0 <= p < n_new[i]:
                     raise StepError(f"step: wanted place {p} is outside the {n_new[i]} tokens given")
-                rows.append(cu[i] + p)
-        positions = np.concatenate([np.arange(o, o + n) for o, n in zip(old, n_new)])
-        tok_seq = np.repeat(np.arange(B), n_new)
-        tables = [cache.page_table(g, slots).numpy() for g in range(len(cache.kv_groups))]
+                rows.append(start + p)
+            start += n_new[i]
+        cache.reserve(dict(zip(slots, new_len)))
+        return _Plan(mode, list(slots), n_new, old, new_len, flat, rows)
 
+    def _context(self, plan: _Plan):
+        cache, B = self.cache, len(plan.slots)
+        T = int(sum(plan.n_new))
+        cu = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(plan.n_new, out=cu[1:])
+        positions = np.concatenate([np.arange(o, o + n) for o, n in zip(plan.old, plan.n_new)])
+        tok_seq = np.repeat(np.arange(B), plan.n_new)
+        tables = [cache.page_table(g, plan.slots).numpy() for g in range(len(cache.kv_groups))]
         # one host buffer, one copy
-        parts = [flat, positions, tok_seq, cu, np.asarray(new_len), np.asarray(slots), np.asarray(rows, dtype=np.int64)]
+        parts = [plan.flat, positions, tok_seq, cu, np.asarray(plan.new_len), np.asarray(plan.slots),
+                 np.asarray(plan.rows, dtype=np.int64)]
         parts += [t.reshape(-1) for t in tables]
         sizes = [p.size for p in parts]
         offs = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])
@@ -114,8 +231,8 @@ class Engine:
         dev = host.to(self.device, non_blocking=True)
         seg = [dev[int(o):int(o) + s] for o, s in zip(offs[:-1], sizes)]
         page_tables = [seg[7 + g].view(B, tables[g].shape[1]) for g in range(len(tables))]
-        ctx = StepContext(mode=mode, dtype=self.model.dtype, device=self.device, cache=cache, batch=B, n_tokens=T,
-                          slots=list(slots), positions=seg[1], tok_seq=seg[2], cu_q=seg[3], kv_len=seg[4],
-                          slots_dev=seg[5], max_q_len=int(max(n_new)), page_tables=page_tables,
-                          host_lengths=new_len)
+        ctx = StepContext(mode=plan.mode, dtype=self.model.dtype, device=self.device, cache=cache, batch=B,
+                          n_tokens=T, slots=plan.slots, positions=seg[1], tok_seq=seg[2], cu_q=seg[3],
+                          kv_len=seg[4], slots_dev=seg[5], max_q_len=int(max(plan.n_new)), page_tables=page_tables,
+                          host_lengths=plan.new_len)
         return ctx, seg[0], seg[6]

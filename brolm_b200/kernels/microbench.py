@@ -1,0 +1,117 @@
+"""Times single kernels of brolm_b200 with CUDA events and prints what they reach.
+
+    python -m brolm_b200.kernels.microbench attn_decode --batch 8 --ctx 8192 [--window 4096]
+    python -m brolm_b200.kernels.microbench attn_prefill --tokens 2048
+    python -m brolm_b200.kernels.microbench norms --batch 8
+
+Sizes default to those of Gemma 2 2B (8 query heads, 4 kv heads of 256).  Inputs
+are larger than the L2 cache or the L2 is flushed between repetitions.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+
+import torch
+
+from . import attention_decode_mma, attention_prefill_mma, decode_splits, residual_rmsnorm, rmsnorm
+
+DEV = "cuda:0"
+
+
+def timed(fn, reps: int, flush=None) -> float:
+    """Median milliseconds of ``fn`` over ``reps`` runs, after three warm-up runs."""
+    for _ in range(3):
+        fn()
+    times = []
+    for _ in range(reps):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    return sorted(times)[len(times) // 2]
+
+
+def attn_decode(args) -> None:
+    B, ctx, n_q, n_kv, hd = args.batch, args.ctx, args.heads, args.kv_heads, args.head_dim
+    ring = (args.window + 63) // 64 * 64 if args.window else 1 << 30
+    per_seq = min((ctx + 63) // 64, ring // 64)
+    pages = B * per_seq
+    kp = torch.randn(pages, n_kv, 64, hd, device=DEV).to(torch.bfloat16)
+    vp = torch.randn(pages, n_kv, 64, hd, device=DEV).to(torch.bfloat16)
+    table = torch.randperm(pages, device=DEV).int().view(B, per_seq).contiguous()
+    q = torch.randn(B, n_q * hd, device=DEV).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    kv_len = torch.full((B,), ctx, dtype=torch.int32, device=DEV)
+    splits = args.splits or decode_splits(B, n_kv, ctx, args.window)
+    n = B * n_q * splits
+    scratch = (torch.empty(n * hd, dtype=torch.float32, device=DEV), torch.empty(n * 2, dtype=torch.float32, device=DEV))
+
+    def run():
+        attention_decode_mma(q, out, cu, kv_len, kp, vp, table, ring=ring, page_size=64, n_kv=n_kv, group=n_q // n_kv,
+                             head_dim=hd, scale=1 / math.sqrt(hd), cap=50.0, window=args.window, batch=B,
+                             n_splits=splits, scratch=scratch)
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    ms = timed(run, args.reps, flush)
+    keys = min(ctx, args.window) if args.window else ctx
+    nbytes = B * keys * n_kv * hd * 2 * 2
+    print(f"attn_decode batch={B} ctx={ctx} window={args.window} splits={splits}: {ms * 1e3:.1f} us, "
+          f"{nbytes / ms / 1e6:.0f} GB/s of cache read")
+
+
+def attn_prefill(args) -> None:
+    T, n_q, n_kv, hd = args.tokens, args.heads, args.kv_heads, args.head_dim
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * hd, device=DEV).to(torch.bfloat16)
+    out = torch.empty(T, n_q * hd, dtype=torch.bfloat16, device=DEV)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+
+    def run():
+        attention_prefill_mma(qkv[:, :n_q * hd], out, cu, qkv[:, n_q * hd:(n_q + n_kv) * hd],
+                              qkv[:, (n_q + n_kv) * hd:], n_kv=n_kv, group=n_q // n_kv, head_dim=hd,
+                              scale=1 / math.sqrt(hd), cap=50.0, window=args.window, batch=1, max_q_len=T)
+
+    ms = timed(run, args.reps)
+    w = args.window or T
+    keys = sum(min(p + 1, w) for p in range(T))
+    flops = 4.0 * n_q * hd * keys
+    print(f"attn_prefill tokens={T} window={args.window}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.1f} TFLOP/s")
+
+
+def norms(args) -> None:
+    B, H = args.batch, args.hidden
+    h = torch.randn(B, H, device=DEV)
+    y = torch.randn(B, H, device=DEV)
+    w = torch.randn(H, device=DEV).to(torch.bfloat16)
+    out = torch.empty(B, H, dtype=torch.bfloat16, device=DEV)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    ms = timed(lambda: residual_rmsnorm(h, y, w, 1e-6, 1.0, w, 1e-6, 1.0, out), args.reps, flush)
+    print(f"residual_rmsnorm rows={B} hidden={H}: {ms * 1e3:.1f} us")
+    ms = timed(lambda: rmsnorm(h, w, 1e-6, 1.0, out), args.reps, flush)
+    print(f"rmsnorm rows={B} hidden={H}: {ms * 1e3:.1f} us")
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "norms"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=8192)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--window", type=int, default=0)
+    ap.add_argument("--heads", type=int, default=8)
+    ap.add_argument("--kv-heads", type=int, default=4)
+    ap.add_argument("--head-dim", type=int, default=256)
+    ap.add_argument("--hidden", type=int, default=2304)
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--reps", type=int, default=20)
+    args = ap.parse_args()
+    {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "norms": norms}[args.what](args)
+
+
+if __name__ == "__main__":
+    main()

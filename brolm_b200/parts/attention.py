@@ -22,6 +22,7 @@ from .linear import linear
 
 class Attention(Part):
     kind = "mixer"
+    graph_safe = True
 
     def __init__(self, hidden: int, n_q: int, n_kv: int, head_dim: int, scale: float, softcap: float = 0.0,
                  window: Optional[int] = None, position: Optional[Part] = None):
@@ -76,7 +77,7 @@ class Attention(Part):
             v = qkv[:, self.q_dim + self.kv_dim:]
             self.attend_packed(q, k, v, out, ctx, common)
         else:
-            if ctx.mode == "prefill" and self.window and max(ctx.host_lengths) > ring:
+            if ctx.mode == "prefill" and self.window and ctx.max_kv_len > ring:
                 raise NotImplementedError("a layer that reads another layer's windowed cache cannot take a "
                                           "prompt longer than the ring in one step")
             self.attend_paged(q, out, ctx, common, k_pages, v_pages, table, ring, page)
@@ -96,7 +97,7 @@ class Attention(Part):
     def attend_paged(self, q, out, ctx, common, k_pages, v_pages, table, ring, page):
         if self._tensor_cores(ctx) and ctx.mode == "decode" and page == 64:
             args = {k: v for k, v in common.items() if k != "max_q_len"}
-            splits = kernels.decode_splits(ctx.batch, self.n_kv, max(ctx.host_lengths), self.window or 0)
+            splits = kernels.decode_splits(ctx.batch, self.n_kv, ctx.max_kv_len, self.window or 0)
             kernels.attention_decode_mma(q, out, ctx.cu_q, ctx.kv_len, k_pages, v_pages, table, ring=ring,
                                          page_size=page, n_splits=splits, **args)
         else:

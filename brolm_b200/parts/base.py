@@ -29,6 +29,10 @@ class Part:
     """Base of all parts."""
 
     kind: str = ""
+    # True when ``forward`` only launches work on the current stream, with
+    # nothing that depends on values read back to the host: the decode step may
+    # then be captured in a CUDA graph and replayed.
+    graph_safe: bool = False
 
     def param_specs(self) -> dict[str, ParamSpec]:
         """Local tensor name -> what it must look like."""

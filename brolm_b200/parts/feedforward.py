@@ -14,6 +14,7 @@ class GatedFeedForward(Part):
     Gate and up run as one product over the rows [Wg; Wu]."""
 
     kind = "feedforward"
+    graph_safe = True
 
     def __init__(self, hidden: int, inter: int, activation: str = "gelu_tanh"):
         if activation not in kernels.ACTIVATIONS:

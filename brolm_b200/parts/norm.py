@@ -18,6 +18,7 @@ class RMSNorm(Part):
     """
 
     kind = "norm"
+    graph_safe = True
 
     def __init__(self, size: int, eps: float, offset: float = 0.0):
         self.size, self.eps, self.offset = size, float(eps), float(offset)
