@@ -223,6 +223,26 @@ class Cache:
                 table[r, :len(l)] = torch.tensor(l, dtype=torch.int32)
         return table
 
+    def write_rows(self, group_id: int, slots: Sequence[int], old: Sequence[int], new: Sequence[int]):
+        """Where each new token of a step goes in a group's storage: one int per
+        token (sequences back to back), page * page_size + place, or -1 for a
+        token the ring will not keep (a later token of the step takes its place)."""
+        import numpy as np
+        g = self.kv_groups[group_id]
+        out = []
+        for s, a, b in zip(slots, old, new):
+            if s < 0:
+                out.append(np.full(b - a, -1, dtype=np.int64))
+                continue
+            pos = np.arange(a, b, dtype=np.int64)
+            ridx = pos % g.ring if g.ring else pos
+            pages = np.asarray(g.pages[s], dtype=np.int64)
+            rows = pages[ridx // g.page_size] * g.page_size + ridx % g.page_size
+            if g.ring:
+                rows[pos < b - g.ring] = -1
+            out.append(rows)
+        return np.concatenate(out) if out else np.zeros(0, dtype=np.int64)
+
     def entry(self, i: int) -> CacheEntry:
         e = self.entries[i]
         if e is None:

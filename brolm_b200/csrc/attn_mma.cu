@@ -518,6 +518,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float sum = 0.0f, acc = 0.0f;
         if (mx > -INFINITY) {
+#pragma unroll 8
             for (int s = 0; s < n_splits; ++s) {
                 const float f = fast_exp2(part_ml[(slot0 + s) * 2] - mx);
                 sum += part_ml[(slot0 + s) * 2 + 1] * f;

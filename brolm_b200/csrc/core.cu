@@ -15,6 +15,7 @@ __global__ void embed_scale_kernel(const int32_t* __restrict__ ids, const W* __r
     const int t = blockIdx.x;
     const W* row = table + (size_t)ids[t] * hidden;
     float* dst = out + (size_t)t * hidden;
+#pragma unroll 4
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(row[i]) * scale;
 }
 
@@ -37,37 +38,105 @@ BROLM_API int brolm_embed_scale(const void* ids, const void* table, int table_dt
 // (src/gemma2.cpp:349; the reference folds the +1 into w at load, :154-175).
 // `rows` (optional) picks the input rows, so that only wanted rows of the
 // final norm are computed.
+//
+// One block per row.  When the width is a multiple of 4 and at most
+// 256 * 4 * MAXC, every thread keeps its share of the row in registers: all
+// loads of the row and of the gain are issued before the first use, so a row
+// costs one trip to memory instead of one per element (a decode step has only
+// a handful of rows, and latency is all there is).
 // ---------------------------------------------------------------------------
-template <typename X, typename W, typename O>
-__global__ void rmsnorm_kernel(const X* __restrict__ x, const int32_t* __restrict__ rows, const W* __restrict__ w,
-                               float eps, float offset, O* __restrict__ out, int hidden) {
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, float (&v)[4]) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
+    uint2 t;
+    *reinterpret_cast<__nv_bfloat162*>(&t.x) = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&t.y) = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = t;
+}
+
+// MAXC = 0: any width, plain loops.
+template <typename X, typename W, typename O, int MAXC>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const X* __restrict__ x, const int32_t* __restrict__ rows,
+                                                      const W* __restrict__ w, float eps, float offset,
+                                                      O* __restrict__ out, int hidden) {
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const X* src = x + (size_t)(rows ? rows[r] : r) * hidden;
-    float ss = 0.0f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float v = to_float(src[i]);
-        ss += v * v;
+    O* dst = out + (size_t)r * hidden;
+    if (MAXC == 0) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float v = to_float(src[i]);
+            ss += v * v;
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = rsqrtf(ss / (float)hidden + eps);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+            dst[i] = from_float<O>(to_float(src[i]) * inv * (offset + to_float(w[i])));
+        return;
     }
+    constexpr int C = MAXC > 0 ? MAXC : 1;
+    float v[C][4], g[C][4];
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int i = (c * 256 + threadIdx.x) * 4;
+        if (i < hidden) { load4(src + i, v[c]); load4(w + i, g[c]); }
+        else { v[c][0] = v[c][1] = v[c][2] = v[c][3] = 0.0f; g[c][0] = g[c][1] = g[c][2] = g[c][3] = 0.0f; }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < C; ++c) ss += v[c][0] * v[c][0] + v[c][1] * v[c][1] + v[c][2] * v[c][2] + v[c][3] * v[c][3];
     ss = block_sum(ss, scratch);
     const float inv = rsqrtf(ss / (float)hidden + eps);
-    O* dst = out + (size_t)r * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-        dst[i] = from_float<O>(to_float(src[i]) * inv * (offset + to_float(w[i])));
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int i = (c * 256 + threadIdx.x) * 4;
+        if (i < hidden) {
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = v[c][e] * inv * (offset + g[c][e]);
+            store4(dst + i, o);
+        }
+    }
+}
+
+static int vec_chunks(int hidden, const void* a, const void* b, const void* c, const void* d) {
+    const uintptr_t bits = (uintptr_t)a | (uintptr_t)b | (uintptr_t)c | (uintptr_t)d;
+    if (hidden % 4 != 0 || (bits & 15)) return 0;
+    if (hidden <= 1024) return 1;
+    if (hidden <= 4096) return 4;
+    if (hidden <= 8192) return 8;
+    return 0;
+}
+
+template <typename X, typename W, typename O>
+static int rmsnorm_launch(const void* x, const void* rows, const void* w, float eps, float offset, void* out, int n,
+                          int hidden, cudaStream_t s) {
+    const int c = vec_chunks(hidden, x, w, out, nullptr);
+#define BROLM_RMS(C) rmsnorm_kernel<X, W, O, C><<<n, 256, 0, s>>>((const X*)x, (const int32_t*)rows, (const W*)w, eps, \
+                                                                  offset, (O*)out, hidden)
+    if (c == 1) BROLM_RMS(1); else if (c == 4) BROLM_RMS(4); else if (c == 8) BROLM_RMS(8); else BROLM_RMS(0);
+#undef BROLM_RMS
+    return launch_status();
 }
 
 template <typename X, typename W>
 static int rmsnorm_out(const void* x, const void* rows, const void* w, float eps, float offset, void* out,
                        int out_dtype, int n, int hidden, cudaStream_t s) {
-    if (out_dtype == BROLM_F32)
-        rmsnorm_kernel<X, W, float><<<n, 256, 0, s>>>((const X*)x, (const int32_t*)rows, (const W*)w, eps, offset,
-                                                      (float*)out, hidden);
-    else if (out_dtype == BROLM_BF16)
-        rmsnorm_kernel<X, W, bf16><<<n, 256, 0, s>>>((const X*)x, (const int32_t*)rows, (const W*)w, eps, offset,
-                                                     (bf16*)out, hidden);
-    else
-        return BROLM_ERR_BAD_DTYPE;
-    return launch_status();
+    if (out_dtype == BROLM_F32) return rmsnorm_launch<X, W, float>(x, rows, w, eps, offset, out, n, hidden, s);
+    if (out_dtype == BROLM_BF16) return rmsnorm_launch<X, W, bf16>(x, rows, w, eps, offset, out, n, hidden, s);
+    return BROLM_ERR_BAD_DTYPE;
 }
 
 BROLM_API int brolm_rmsnorm(const void* x, int x_dtype, const void* rows, const void* w, int w_dtype, float eps,
@@ -88,41 +157,108 @@ BROLM_API int brolm_rmsnorm(const void* x, int x_dtype, const void* rows, const 
 // Residual sum with the norms around it, one pass over the row:
 //     h += post ? rmsnorm(y; w_post) : y          (src/gemma2.cpp:372-373, 385-386)
 //     out = rmsnorm(h; w_next)   if w_next        (src/gemma2.cpp:376, :349 of the next layer)
-// h is the float residual stream.
+// h is the float residual stream.  Same register scheme as above.
 // ---------------------------------------------------------------------------
-template <typename Y, typename W, typename O>
-__global__ void residual_rmsnorm_kernel(float* __restrict__ h, const Y* __restrict__ y, const W* __restrict__ w_post,
-                                        float eps_post, float off_post, const W* __restrict__ w_next, float eps_next,
-                                        float off_next, O* __restrict__ out, int hidden) {
+template <typename Y, typename W, typename O, int MAXC>
+__global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict__ h, const Y* __restrict__ y,
+                                                               const W* __restrict__ w_post, float eps_post,
+                                                               float off_post, const W* __restrict__ w_next,
+                                                               float eps_next, float off_next, O* __restrict__ out,
+                                                               int hidden) {
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     float* hr = h + (size_t)r * hidden;
     const Y* yr = y + (size_t)r * hidden;
-    float inv_post = 1.0f;
+    O* dst = out + (size_t)r * hidden;
+    if (MAXC == 0) {
+        float inv_post = 1.0f;
+        if (w_post) {
+            float ss = 0.0f;
+            for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+                const float v = to_float(yr[i]);
+                ss += v * v;
+            }
+            ss = block_sum(ss, scratch);
+            inv_post = rsqrtf(ss / (float)hidden + eps_post);
+        }
+        float ss2 = 0.0f;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            float v = to_float(yr[i]);
+            if (w_post) v = v * inv_post * (off_post + to_float(w_post[i]));
+            const float s = hr[i] + v;
+            hr[i] = s;
+            ss2 += s * s;
+        }
+        if (!w_next) return;
+        ss2 = block_sum(ss2, scratch);
+        const float inv_next = rsqrtf(ss2 / (float)hidden + eps_next);
+        // every thread reads back only what it wrote itself
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+            dst[i] = from_float<O>(hr[i] * inv_next * (off_next + to_float(w_next[i])));
+        return;
+    }
+    constexpr int C = MAXC > 0 ? MAXC : 1;
+    float v[C][4], res[C][4], gp[C][4], gn[C][4];
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int i = (c * 256 + threadIdx.x) * 4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[c][e] = res[c][e] = gp[c][e] = gn[c][e] = 0.0f;
+        if (i < hidden) {
+            load4(yr + i, v[c]);
+            load4(hr + i, res[c]);
+            if (w_post) load4(w_post + i, gp[c]);
+            if (w_next) load4(w_next + i, gn[c]);
+        }
+    }
     if (w_post) {
         float ss = 0.0f;
-        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-            const float v = to_float(yr[i]);
-            ss += v * v;
-        }
+#pragma unroll
+        for (int c = 0; c < C; ++c) ss += v[c][0] * v[c][0] + v[c][1] * v[c][1] + v[c][2] * v[c][2] + v[c][3] * v[c][3];
         ss = block_sum(ss, scratch);
-        inv_post = rsqrtf(ss / (float)hidden + eps_post);
+        const float inv_post = rsqrtf(ss / (float)hidden + eps_post);
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[c][e] = v[c][e] * inv_post * (off_post + gp[c][e]);
     }
     float ss2 = 0.0f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        float v = to_float(yr[i]);
-        if (w_post) v = v * inv_post * (off_post + to_float(w_post[i]));
-        const float s = hr[i] + v;
-        hr[i] = s;
-        ss2 += s * s;
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int i = (c * 256 + threadIdx.x) * 4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            res[c][e] += v[c][e];
+            ss2 += res[c][e] * res[c][e];
+        }
+        if (i < hidden) store4(hr + i, res[c]);
     }
     if (!w_next) return;
     ss2 = block_sum(ss2, scratch);
     const float inv_next = rsqrtf(ss2 / (float)hidden + eps_next);
-    O* dst = out + (size_t)r * hidden;
-    // every thread reads back only what it wrote itself
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-        dst[i] = from_float<O>(hr[i] * inv_next * (off_next + to_float(w_next[i])));
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int i = (c * 256 + threadIdx.x) * 4;
+        if (i < hidden) {
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = res[c][e] * inv_next * (off_next + gn[c][e]);
+            store4(dst + i, o);
+        }
+    }
+}
+
+template <typename Y, typename W, typename O>
+static int residual_launch(void* h, const void* y, const void* w_post, float eps_post, float off_post,
+                           const void* w_next, float eps_next, float off_next, void* out, int n, int hidden,
+                           cudaStream_t s) {
+    int c = vec_chunks(hidden, h, y, w_post, w_next);
+    if (c && ((uintptr_t)out & 15)) c = 0;
+#define BROLM_RES(C) residual_rmsnorm_kernel<Y, W, O, C><<<n, 256, 0, s>>>((float*)h, (const Y*)y, (const W*)w_post, \
+        eps_post, off_post, (const W*)w_next, eps_next, off_next, (O*)out, hidden)
+    if (c == 1) BROLM_RES(1); else if (c == 4) BROLM_RES(4); else if (c == 8) BROLM_RES(8); else BROLM_RES(0);
+#undef BROLM_RES
+    return launch_status();
 }
 
 template <typename Y, typename W>
@@ -130,16 +266,10 @@ static int residual_out(void* h, const void* y, const void* w_post, float eps_po
                         const void* w_next, float eps_next, float off_next, void* out, int out_dtype, int n,
                         int hidden, cudaStream_t s) {
     if (out_dtype == BROLM_F32)
-        residual_rmsnorm_kernel<Y, W, float><<<n, 256, 0, s>>>((float*)h, (const Y*)y, (const W*)w_post, eps_post,
-                                                               off_post, (const W*)w_next, eps_next, off_next,
-                                                               (float*)out, hidden);
-    else if (out_dtype == BROLM_BF16)
-        residual_rmsnorm_kernel<Y, W, bf16><<<n, 256, 0, s>>>((float*)h, (const Y*)y, (const W*)w_post, eps_post,
-                                                              off_post, (const W*)w_next, eps_next, off_next,
-                                                              (bf16*)out, hidden);
-    else
-        return BROLM_ERR_BAD_DTYPE;
-    return launch_status();
+        return residual_launch<Y, W, float>(h, y, w_post, eps_post, off_post, w_next, eps_next, off_next, out, n, hidden, s);
+    if (out_dtype == BROLM_BF16)
+        return residual_launch<Y, W, bf16>(h, y, w_post, eps_post, off_post, w_next, eps_next, off_next, out, n, hidden, s);
+    return BROLM_ERR_BAD_DTYPE;
 }
 
 // w_post and w_next share one element type (w_dtype); either may be null.
@@ -173,71 +303,68 @@ BROLM_API int brolm_residual_rmsnorm(void* h, const void* y, int y_dtype, const 
 // double (src/gemma2.cpp:355-356; pairing as stored in the checkpoint, which
 // include/brolm/detail/weights.h:106-127 permutes instead).
 //
-// Token t belongs to batch row tok_seq[t] and stands at positions[t]; a
-// negative position marks a padding row, which is left untouched.  The cache
-// of this layer is k_pages/v_pages [page][kv_head][page_size][hd]; position p
-// lives at ring index p % ring in page page_table[row][(p % ring)/page_size].
-// Positions older than kv_len[row] - ring are not written: a later position of
-// the same step owns their place.
+// A negative position marks a padding row, which is left untouched.  The cache
+// of this layer is k_pages/v_pages [page][kv_head][page_size][hd];
+// cache_rows[t] = page * page_size + place says where token t goes, a negative
+// value that it is not kept (a later position of the same step owns its place
+// in the ring).  One block per (token, head), one pair of elements per thread:
+// every load of a token is issued at once.
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int32_t* __restrict__ positions,
-                                     const int32_t* __restrict__ tok_seq, const float2* __restrict__ cos_sin,
-                                     int n_q, int n_kv, int hd, int rot, T* __restrict__ k_pages,
-                                     T* __restrict__ v_pages, const int32_t* __restrict__ page_table, int pt_stride,
-                                     const int32_t* __restrict__ kv_len, int ring, int page_size) {
-    const int t = blockIdx.x;
+                                     const float2* __restrict__ cos_sin, int n_q, int n_kv, int hd, int rot,
+                                     T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                     const int32_t* __restrict__ cache_rows, int page_size) {
+    const int t = blockIdx.x, head = blockIdx.y;          // head: q heads, then k heads, then v heads
     const int pos = positions[t];
     if (pos < 0) return;
-    const int row_stride = (n_q + 2 * n_kv) * hd;
-    T* row = qkv + (size_t)t * row_stride;
-    const int half = rot >> 1;
-
-    if (cos_sin) {
-        const float2* cs = cos_sin + (size_t)pos * half;
-        const int pairs = (n_q + n_kv) * half;
-        for (int idx = threadIdx.x; idx < pairs; idx += blockDim.x) {
-            const int head = idx / half, i = idx - head * half;
-            T* p = row + head * hd;
-            const float a = to_float(p[i]), b = to_float(p[i + half]);
-            const float2 c = cs[i];
-            p[i] = from_float<T>(a * c.x - b * c.y);
-            p[i + half] = from_float<T>(a * c.y + b * c.x);
-        }
+    const bool is_v = head >= n_q + n_kv, is_k = !is_v && head >= n_q;
+    const bool rotate = !is_v && cos_sin != nullptr;
+    if (!rotate && !((is_k || is_v) && k_pages)) return;  // nothing to do for this head
+    const int crow = (k_pages && (is_k || is_v)) ? cache_rows[t] : -1;
+    if (is_v && crow < 0) return;
+    T* p = qkv + (size_t)t * (n_q + 2 * n_kv) * hd + (size_t)head * hd;
+    T* dst = nullptr;
+    if (crow >= 0) {
+        const int g = is_k ? head - n_q : head - n_q - n_kv;
+        T* pages = is_k ? k_pages : v_pages;
+        dst = pages + (((size_t)(crow / page_size) * n_kv + g) * page_size + crow % page_size) * hd;
     }
-    if (!k_pages) return;
-    const int b = tok_seq[t];
-    if (pos < kv_len[b] - ring) return;
-    __syncthreads();   // the rotated k of this row is complete
-    const int ridx = pos % ring;
-    const int page = page_table[(size_t)b * pt_stride + ridx / page_size];
-    const int off = ridx % page_size;
-    const T* ksrc = row + n_q * hd;
-    const T* vsrc = ksrc + n_kv * hd;
-    for (int idx = threadIdx.x; idx < n_kv * hd; idx += blockDim.x) {
-        const int g = idx / hd, d = idx - g * hd;
-        const size_t dst = (((size_t)page * n_kv + g) * page_size + off) * hd + d;
-        k_pages[dst] = ksrc[idx];
-        v_pages[dst] = vsrc[idx];
+    const int half = rot >> 1;
+    for (int j = threadIdx.x; j < (hd >> 1); j += blockDim.x) {
+        // the two elements of this thread: a rotated pair, or two elements past the rotated part
+        const bool in_rot = j < half;
+        const int e0 = in_rot ? j : rot + 2 * (j - half), e1 = in_rot ? j + half : e0 + 1;
+        T a = p[e0], b = p[e1];
+        if (rotate && in_rot) {
+            const float2 c = cos_sin[(size_t)pos * half + j];
+            const float fa = to_float(a), fb = to_float(b);
+            a = from_float<T>(fa * c.x - fb * c.y);
+            b = from_float<T>(fa * c.y + fb * c.x);
+            p[e0] = a;
+            p[e1] = b;
+        }
+        if (dst) { dst[e0] = a; dst[e1] = b; }
     }
 }
 
-BROLM_API int brolm_rope_kv_write(void* qkv, int dtype, const void* positions, const void* tok_seq,
-                                  const void* cos_sin, int n_q, int n_kv, int hd, int rot, void* k_pages,
-                                  void* v_pages, const void* page_table, int pt_stride, const void* kv_len, int ring,
+BROLM_API int brolm_rope_kv_write(void* qkv, int dtype, const void* positions, const void* cos_sin, int n_q, int n_kv,
+                                  int hd, int rot, void* k_pages, void* v_pages, const void* cache_rows,
                                   int page_size, int tokens, cudaStream_t stream) {
     if (tokens <= 0) return BROLM_OK;
-    if (rot > hd || (rot & 1) || ring <= 0 || page_size <= 0 || ring % page_size != 0) return BROLM_ERR_BAD_SIZE;
+    if (rot > hd || (rot & 1) || (hd & 1) || page_size <= 0) return BROLM_ERR_BAD_SIZE;
+    if (n_q + 2 * n_kv > 65535) return BROLM_ERR_TOO_LARGE;
+    dim3 grid(tokens, n_q + 2 * n_kv);
+    int threads = ((hd >> 1) + 31) / 32 * 32;
+    if (threads > 256) threads = 256;
     if (dtype == BROLM_F32)
-        rope_kv_write_kernel<float><<<tokens, 256, 0, stream>>>(
-            (float*)qkv, (const int32_t*)positions, (const int32_t*)tok_seq, (const float2*)cos_sin, n_q, n_kv, hd,
-            rot, (float*)k_pages, (float*)v_pages, (const int32_t*)page_table, pt_stride, (const int32_t*)kv_len,
-            ring, page_size);
+        rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>(
+            (float*)qkv, (const int32_t*)positions, (const float2*)cos_sin, n_q, n_kv, hd, rot, (float*)k_pages,
+            (float*)v_pages, (const int32_t*)cache_rows, page_size);
     else if (dtype == BROLM_BF16)
-        rope_kv_write_kernel<bf16><<<tokens, 256, 0, stream>>>(
-            (bf16*)qkv, (const int32_t*)positions, (const int32_t*)tok_seq, (const float2*)cos_sin, n_q, n_kv, hd,
-            rot, (bf16*)k_pages, (bf16*)v_pages, (const int32_t*)page_table, pt_stride, (const int32_t*)kv_len, ring,
-            page_size);
+        rope_kv_write_kernel<bf16><<<grid, threads, 0, stream>>>(
+            (bf16*)qkv, (const int32_t*)positions, (const float2*)cos_sin, n_q, n_kv, hd, rot, (bf16*)k_pages,
+            (bf16*)v_pages, (const int32_t*)cache_rows, page_size);
     else
         return BROLM_ERR_BAD_DTYPE;
     return launch_status();

@@ -36,9 +36,23 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict
     const float* row = logits + (size_t)blockIdx.x * vocab;
     float best = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+    if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        // four values a load, four loads in flight: the row is read in a few trips to memory
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const int n4 = vocab >> 2;
+#pragma unroll 4
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            const float4 v = row4[i];
+            const float vs[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (vs[e] > best) { best = vs[e]; idx = 4 * i + e; }     // ids rise within a thread: the first maximum stays
+        }
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const float v = row[i];
+            if (v > best) { best = v; idx = i; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {

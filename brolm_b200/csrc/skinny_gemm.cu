@@ -1,0 +1,215 @@
+// Matrix product for a handful of tokens:  Y[M,N] = X[M,K] * W[N,K]^T with
+// M <= 16, bfloat16 operands, float accumulation (decode steps).
+//
+// With so few tokens the product only has to stream W from memory once, so
+// the kernel is built around that stream.  The roles of the operands are
+// swapped for the tensor cores: 16 rows of W fill the M side of an
+// mma.sync m16n8k16, 8 tokens fill the N side.  Every thread fetches its
+// fragments with 16-byte loads straight from global memory: the four lanes
+// of a quad read 8 consecutive k each (32 k in all), which is two k16 steps
+// of the instruction under a fixed permutation of k that X is loaded with as
+// well, so no shared memory or ldmatrix is needed on the way in.
+//
+// A block owns a few 16-row tiles of W over the whole of K; its 8 warps take
+// interleaved 64-wide blocks of K with the next block's loads in flight, and
+// add their partial sums in shared memory in warp order (the result does not
+// depend on scheduling).  Epilogues: plain store (bfloat16 or float), the
+// gated activation act(gate) * up for W = [Wg; Wu] (wlejon/brolm
+// src/gemma2.cpp:378-381), or cap * tanh(y / cap) into float logits
+// (src/gemma2.cpp:406-412).
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int KB = 64;     // k per warp iteration
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg16(const bf16* p, bool ok) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (ok) asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ldg16_cached(const bf16* p, bool ok) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (ok) v = *reinterpret_cast<const uint4*>(p);
+    return v;
+}
+
+__device__ __forceinline__ float act_apply(float z, int act) {
+    if (act == 0) {
+        const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+        return 0.5f * z * (1.0f + tanhf(u));
+    }
+    return z / (1.0f + expf(-z));
+}
+
+enum : int { EPI_STORE = 0, EPI_GATED = 1, EPI_SOFTCAP = 2 };
+
+struct SkinnyArgs {
+    const bf16* x;
+    const bf16* w;
+    void* y;
+    int ldx, ldw, ldy;
+    int M, N, K;          // N: rows of W used as outputs (EPI_GATED: W has 2N rows, gate then up)
+    int out_f32;
+    int act;
+    float cap;
+};
+
+// MT: 16-row tiles of W per block.  NT: 8-token tiles.
+template <int MT, int NT, int EPI>
+__global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
+    __shared__ float red[WARPS][MT * NT * 4][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int q = lane & 3, r = lane >> 2;
+    constexpr int OUT_TILES = EPI == EPI_GATED ? MT / 2 : MT;      // 16-column tiles of Y per block
+    const int n0 = blockIdx.x * OUT_TILES * 16;
+
+    // first row of W of each tile
+    int wrow[MT];
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+        wrow[i] = EPI == EPI_GATED ? ((i & 1) ? a.N : 0) + n0 + 16 * (i >> 1) : n0 + 16 * i;
+    const int w_rows = EPI == EPI_GATED ? 2 * a.N : a.N;
+    const int n_limit = a.N;                                       // output columns that exist
+
+    float acc[MT][NT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.0f;
+
+    const int nkb = (a.K + KB - 1) / KB;
+    uint4 wc[2][MT][2], xc[2][NT];                                 // [half of the block][tile][row r / r + 8]
+
+    auto load = [&](int kb, uint4 (&wv)[2][MT][2], uint4 (&xv)[2][NT]) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int kk = kb * KB + h * 32 + q * 8;
+            const bool kok = kk < a.K;                              // K is a multiple of 8
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+                const int col = (EPI == EPI_GATED ? wrow[i] - ((i & 1) ? a.N : 0) : wrow[i]) + r;   // output column of row r
+                wv[h][i][0] = ldg16(a.w + (size_t)(wrow[i] + r) * a.ldw + kk, kok && col < n_limit);
+                wv[h][i][1] = ldg16(a.w + (size_t)(wrow[i] + r + 8) * a.ldw + kk, kok && col + 8 < n_limit);
+            }
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const int tok = j * 8 + r;
+                xv[h][j] = ldg16_cached(a.x + (size_t)tok * a.ldx + kk, kok && tok < a.M);
+            }
+        }
+    };
+    (void)w_rows;
+
+    int kb = warp;
+    if (kb < nkb) load(kb, wc, xc);
+    for (; kb < nkb; kb += WARPS) {
+        uint4 wn[2][MT][2], xn[2][NT];
+        const bool more = kb + WARPS < nkb;
+        if (more) load(kb + WARPS, wn, xn);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    mma_bf16(acc[i][j], wc[h][i][0].x, wc[h][i][1].x, wc[h][i][0].y, wc[h][i][1].y, xc[h][j].x, xc[h][j].y);
+                    mma_bf16(acc[i][j], wc[h][i][0].z, wc[h][i][1].z, wc[h][i][0].w, wc[h][i][1].w, xc[h][j].z, xc[h][j].w);
+                }
+            }
+        }
+        if (more) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int i = 0; i < MT; ++i) { wc[h][i][0] = wn[h][i][0]; wc[h][i][1] = wn[h][i][1]; }
+#pragma unroll
+                for (int j = 0; j < NT; ++j) xc[h][j] = xn[h][j];
+            }
+        }
+    }
+
+    // partial sums of the warps -> shared memory, then summed in warp order
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) red[warp][(i * NT + j) * 4 + e][lane] = acc[i][j][e];
+    __syncthreads();
+
+    constexpr int OUT_ELEMS = OUT_TILES * NT * 4 * 32;
+    for (int idx = threadIdx.x; idx < OUT_ELEMS; idx += WARPS * 32) {
+        const int ln = idx & 31, e = (idx >> 5) & 3, j = (idx >> 7) % NT, ot = (idx >> 7) / NT;
+        const int col = n0 + ot * 16 + (ln >> 2) + ((e >> 1) << 3);
+        const int tok = j * 8 + (ln & 3) * 2 + (e & 1);
+        float v;
+        if (EPI == EPI_GATED) {
+            float gsum = 0.0f, usum = 0.0f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                gsum += red[w][((2 * ot) * NT + j) * 4 + e][ln];
+                usum += red[w][((2 * ot + 1) * NT + j) * 4 + e][ln];
+            }
+            v = act_apply(gsum, a.act) * usum;
+        } else {
+            v = 0.0f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) v += red[w][(ot * NT + j) * 4 + e][ln];
+            if (EPI == EPI_SOFTCAP) v = soft_cap(v, a.cap);
+        }
+        if (col < n_limit && tok < a.M) {
+            if (a.out_f32) reinterpret_cast<float*>(a.y)[(size_t)tok * a.ldy + col] = v;
+            else reinterpret_cast<bf16*>(a.y)[(size_t)tok * a.ldy + col] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+template <int MT, int NT, int EPI>
+int launch(const SkinnyArgs& a, cudaStream_t stream) {
+    constexpr int cols = (EPI == EPI_GATED ? MT / 2 : MT) * 16;
+    const int blocks = (a.N + cols - 1) / cols;
+    skinny_kernel<MT, NT, EPI><<<blocks, WARPS * 32, 0, stream>>>(a);
+    return launch_status();
+}
+
+template <int EPI>
+int dispatch(const SkinnyArgs& a, int mt, cudaStream_t stream) {
+    const int nt = (a.M + 7) / 8;
+    if (EPI == EPI_GATED) {
+        if (nt == 1) return mt >= 4 ? launch<4, 1, EPI>(a, stream) : launch<2, 1, EPI>(a, stream);
+        return mt >= 4 ? launch<4, 2, EPI>(a, stream) : launch<2, 2, EPI>(a, stream);
+    }
+    if (nt == 1) return mt >= 4 ? launch<4, 1, EPI>(a, stream) : mt >= 2 ? launch<2, 1, EPI>(a, stream) : launch<1, 1, EPI>(a, stream);
+    return mt >= 4 ? launch<4, 2, EPI>(a, stream) : mt >= 2 ? launch<2, 2, EPI>(a, stream) : launch<1, 2, EPI>(a, stream);
+}
+
+}  // namespace
+
+// epilogue 0: Y = X W^T (bfloat16, or float when out_f32); 1: Y = act(X Wg^T) * (X Wu^T) with
+// W = [Wg; Wu] of 2N rows; 2: Y = cap * tanh(X W^T / cap), float.  M <= 16; K a multiple of 8;
+// rows of X and W 16-byte aligned.  tiles: 16-row tiles of W per block (1, 2 or 4).
+BROLM_API int brolm_skinny_gemm(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int M, int N, int K,
+                                int epilogue, int out_f32, int act, float cap, int tiles, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return BROLM_OK;
+    if (M > 16) return BROLM_ERR_TOO_LARGE;
+    if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return BROLM_ERR_ALIGNMENT;
+    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return BROLM_ERR_ALIGNMENT;
+    if (epilogue == EPI_GATED && (act < 0 || act > 1)) return BROLM_ERR_BAD_SIZE;
+    SkinnyArgs a;
+    a.x = (const bf16*)x; a.w = (const bf16*)w; a.y = y; a.ldx = ldx; a.ldw = ldw; a.ldy = ldy;
+    a.M = M; a.N = N; a.K = K; a.out_f32 = out_f32; a.act = act; a.cap = cap;
+    if (epilogue == EPI_STORE) return dispatch<EPI_STORE>(a, tiles, stream);
+    if (epilogue == EPI_GATED) return dispatch<EPI_GATED>(a, tiles, stream);
+    if (epilogue == EPI_SOFTCAP) { a.out_f32 = 1; return dispatch<EPI_SOFTCAP>(a, tiles, stream); }
+    return BROLM_ERR_BAD_SIZE;
+}

@@ -32,6 +32,7 @@ class StepContext:
     slots_dev: torch.Tensor        # int32 [batch]
     max_q_len: int
     page_tables: list              # per key/value group: int32 [batch, width] on the device
+    cache_rows: list               # per key/value group: int32 [n_tokens], page * page_size + place, or -1
     host_lengths: list             # host copy of kv_len
     max_kv_len: int = 0            # an upper bound of kv_len for sizing launches (a captured graph fixes it)
 

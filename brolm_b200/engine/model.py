@@ -158,9 +158,14 @@ class DecoderModel:
             return torch.empty((0, lay.embedding.vocab), dtype=torch.float32, device=self.device)
         head_in = torch.float32 if self.head.dtype == torch.float32 else self.dtype
         xf = self.final_norm.apply(h, head_in, rows=rows)
+        cap = float(lay.head.softcap or 0.0)
+        if kernels.skinny_ok(xf, self.head):
+            logits = torch.empty((xf.shape[0], self.head.shape[0]), dtype=torch.float32, device=self.device)
+            kernels.skinny_gemm(xf, self.head, logits, "softcap" if cap > 0 else "store", cap=cap)
+            return logits
         logits = linear(xf, self.head, out_dtype=torch.float32)
-        if lay.head.softcap and lay.head.softcap > 0:
-            kernels.softcap(logits, logits, float(lay.head.softcap))
+        if cap > 0:
+            kernels.softcap(logits, logits, cap)
         return logits
 
 

@@ -60,7 +60,7 @@ class _DecodeGraph:
             if g.ring:
                 w = min(w, g.ring // g.page_size)
             self.widths.append(max(1, w))
-        n = 4 * rows + sum(rows * w for w in self.widths)
+        n = 4 * rows + sum(rows * w for w in self.widths) + rows * len(self.widths)
         self.host = torch.zeros(n, dtype=torch.int32, pin_memory=True)
         self.hv = self.host.numpy()
         self.dev = torch.zeros(n, dtype=torch.int32, device=dev)
@@ -70,17 +70,19 @@ class _DecodeGraph:
         for w in self.widths:
             tables.append(self.dev[off:off + rows * w].view(rows, w))
             off += rows * w
+        self.rows_off = off
+        cache_rows = [self.dev[off + g * rows:off + (g + 1) * rows] for g in range(len(self.widths))]
         self.tokens = seg[0]
         ar = torch.arange(rows + 1, dtype=torch.int32, device=dev)
         self.ctx = StepContext(
             mode="decode", dtype=engine.model.dtype, device=dev, cache=cache, batch=rows, n_tokens=rows, slots=[],
             positions=seg[1], tok_seq=ar[:rows].clone(), cu_q=ar, kv_len=seg[2], slots_dev=seg[3], max_q_len=1,
-            page_tables=tables, host_lengths=[], max_kv_len=kv_cap)
+            page_tables=tables, cache_rows=cache_rows, host_lengths=[], max_kv_len=kv_cap)
         self.all_rows = ar[:rows].clone()
         # an all-padding state: the warm-up pass touches no cache
         self.hv[:] = 0
         self.hv[rows:2 * rows] = -1
-        self.hv[3 * rows:4 * rows] = 0
+        self.hv[self.rows_off:] = -1
         self.dev.copy_(self.host)
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
@@ -109,6 +111,9 @@ class _DecodeGraph:
             t = cache.page_table(g, plan.slots, width=w, rows=R)
             hv[off:off + R * w] = t.numpy().reshape(-1)
             off += R * w
+        hv[off:] = -1
+        for g in range(len(self.widths)):
+            hv[off + g * R:off + g * R + B] = cache.write_rows(g, plan.slots, plan.old, plan.new_len)
         self.dev.copy_(self.host, non_blocking=True)
         self.copied.record()
         self.graph.replay()
@@ -222,6 +227,7 @@ class Engine:
         parts = [plan.flat, positions, tok_seq, cu, np.asarray(plan.new_len), np.asarray(plan.slots),
                  np.asarray(plan.rows, dtype=np.int64)]
         parts += [t.reshape(-1) for t in tables]
+        parts += [cache.write_rows(g, plan.slots, plan.old, plan.new_len) for g in range(len(tables))]
         sizes = [p.size for p in parts]
         offs = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])
         host = torch.zeros(int(offs[-1]), dtype=torch.int32, pin_memory=self.device.type == "cuda")
@@ -231,8 +237,9 @@ class Engine:
         dev = host.to(self.device, non_blocking=True)
         seg = [dev[int(o):int(o) + s] for o, s in zip(offs[:-1], sizes)]
         page_tables = [seg[7 + g].view(B, tables[g].shape[1]) for g in range(len(tables))]
+        cache_rows = [seg[7 + len(tables) + g] for g in range(len(tables))]
         ctx = StepContext(mode=plan.mode, dtype=self.model.dtype, device=self.device, cache=cache, batch=B,
                           n_tokens=T, slots=plan.slots, positions=seg[1], tok_seq=seg[2], cu_q=seg[3],
                           kv_len=seg[4], slots_dev=seg[5], max_q_len=int(max(plan.n_new)), page_tables=page_tables,
-                          host_lengths=plan.new_len)
+                          cache_rows=cache_rows, host_lengths=plan.new_len)
         return ctx, seg[0], seg[6]

@@ -127,31 +127,28 @@ def residual_rmsnorm(h: torch.Tensor, y: torch.Tensor, post_weight: Optional[tor
            "residual_rmsnorm")
 
 
-def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, tok_seq: Optional[torch.Tensor],
-                  cos_sin: Optional[torch.Tensor], n_q: int, n_kv: int, head_dim: int, rotary_dim: int,
-                  k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
-                  page_table: Optional[torch.Tensor], kv_len: Optional[torch.Tensor], ring: int,
-                  page_size: int) -> None:
-    """Rotate q and k inside qkv (tokens, (n_q + 2 n_kv) * head_dim) and write k, v into the cache pages."""
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: Optional[torch.Tensor], n_q: int, n_kv: int,
+                  head_dim: int, rotary_dim: int, k_pages: Optional[torch.Tensor] = None,
+                  v_pages: Optional[torch.Tensor] = None, cache_rows: Optional[torch.Tensor] = None,
+                  page_size: int = 64) -> None:
+    """Rotate q and k inside qkv (tokens, (n_q + 2 n_kv) * head_dim) and write k, v into the cache pages.
+
+    ``cache_rows[t]`` = page * page_size + place of token t, negative when the token is not kept."""
     assert qkv.is_contiguous() and qkv.shape[1] == (n_q + 2 * n_kv) * head_dim
     assert positions.dtype == torch.int32 and positions.numel() == qkv.shape[0]
-    pt_stride = 0
     if k_pages is not None:
-        assert v_pages is not None and page_table is not None and kv_len is not None and tok_seq is not None
+        assert v_pages is not None and cache_rows is not None
         assert k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype
         assert k_pages.is_contiguous() and v_pages.is_contiguous()
         assert tuple(k_pages.shape[1:]) == (n_kv, page_size, head_dim), (k_pages.shape, n_kv, page_size, head_dim)
-        assert page_table.dtype == torch.int32 and page_table.dim() == 2 and page_table.stride(1) == 1
-        assert kv_len.dtype == torch.int32 and tok_seq.dtype == torch.int32
-        pt_stride = page_table.stride(0)
+        assert cache_rows.dtype == torch.int32 and cache_rows.numel() == qkv.shape[0]
     if cos_sin is not None:
         assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1:] == (rotary_dim // 2, 2)
-    f = _fn("core", "brolm_rope_kv_write", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                            c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-                                            c_void_p])
-    _check(f(_ptr(qkv), _code(qkv), _ptr(positions), _ptr(tok_seq), _ptr(cos_sin), n_q, n_kv, head_dim, rotary_dim,
-             _ptr(k_pages), _ptr(v_pages), _ptr(page_table), pt_stride, _ptr(kv_len), ring, page_size,
-             qkv.shape[0], _stream()), "rope_kv_write")
+    f = _fn("core", "brolm_rope_kv_write", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                            c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(qkv), _code(qkv), _ptr(positions), _ptr(cos_sin), n_q, n_kv, head_dim, rotary_dim, _ptr(k_pages),
+             _ptr(v_pages), _ptr(cache_rows) if k_pages is not None else None, page_size, qkv.shape[0], _stream()),
+           "rope_kv_write")
 
 
 def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
@@ -184,6 +181,45 @@ def linear_f32(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None
                                                c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K, _stream()),
            "linear_f32")
+
+
+SKINNY_MAX_ROWS = 16
+
+
+def skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether the few-token product kernel takes these operands."""
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and
+            0 < x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(1) == 1 and
+            x.stride(0) % 8 == 0 and weight.stride(1) == 1 and weight.stride(0) % 8 == 0 and
+            x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "store",
+                activation: str = "gelu_tanh", cap: float = 0.0) -> None:
+    """out = x @ weight^T for at most 16 rows of x (bfloat16 in, float32 accumulation).
+
+    ``epilogue``: "store" (out bfloat16 or float32), "gated" (weight = [Wg; Wu],
+    out = act(x Wg^T) * (x Wu^T)), "softcap" (out float32 = cap * tanh(. / cap)).
+    """
+    assert skinny_ok(x, weight) and out.stride(1) == 1 and out.shape[0] == x.shape[0]
+    M, K = x.shape
+    assert weight.shape[1] == K
+    code = {"store": 0, "gated": 1, "softcap": 2}[epilogue]
+    N = out.shape[1]
+    assert weight.shape[0] == (2 * N if code == 1 else N)
+    if code == 1:
+        if activation not in ACTIVATIONS:
+            raise KernelError(f"skinny_gemm: unknown activation '{activation}'")
+        tiles = 4 if N >= 32 * 296 else 2
+    else:
+        tiles = 4 if N >= 64 * 296 else 2 if N >= 32 * 296 else 1
+    if code == 2:
+        assert out.dtype == torch.float32
+    f = _fn("skinny_gemm", "brolm_skinny_gemm", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                                 c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K, code,
+             1 if out.dtype == torch.float32 else 0, ACTIVATIONS.get(activation, 0), cap, tiles, _stream()),
+           "skinny_gemm")
 
 
 def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor, *, n_kv: int,
@@ -285,5 +321,5 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
 
 
 __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "embed_scale", "rmsnorm", "residual_rmsnorm",
-           "rope_kv_write", "gated_act", "softcap", "linear_f32", "attention_simt", "attention_prefill_mma", "attention_decode_mma",
+           "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_ok", "attention_simt", "attention_prefill_mma", "attention_decode_mma",
            "decode_splits", "argmax", "sample"]

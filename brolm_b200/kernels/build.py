@@ -34,6 +34,7 @@ LIBRARIES: dict[str, list[str]] = {
     "linear_f32": ["linear_f32.cu"],
     "attn_simt": ["attn_simt.cu"],
     "attn_mma": ["attn_mma.cu"],
+    "skinny_gemm": ["skinny_gemm.cu"],
     "sampling": ["sampling.cu"],
 }
 HEADERS = ["common.cuh"]

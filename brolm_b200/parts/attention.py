@@ -63,9 +63,10 @@ class Attention(Part):
         k_pages, v_pages, table, ring, page = ctx.kv(entry)
         rot = self.position.rotary_dim if self.position is not None else 0
         kernels.rope_kv_write(
-            qkv, ctx.positions, ctx.tok_seq, self.position.table if self.position is not None else None,
+            qkv, ctx.positions, self.position.table if self.position is not None else None,
             self.n_q, self.n_kv, self.head_dim, rot,
-            k_pages if writes_cache else None, v_pages if writes_cache else None, table, ctx.kv_len, ring, page)
+            k_pages if writes_cache else None, v_pages if writes_cache else None,
+            ctx.cache_rows[entry.group_id] if writes_cache else None, page)
         q = qkv[:, :self.q_dim]
         out = torch.empty((qkv.shape[0], self.q_dim), dtype=ctx.dtype, device=x.device)
         common = dict(n_kv=self.n_kv, group=self.n_q // self.n_kv, head_dim=self.head_dim, scale=self.scale,

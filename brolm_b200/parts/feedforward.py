@@ -34,9 +34,13 @@ class GatedFeedForward(Part):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         """x (tokens, hidden) -> (tokens, hidden) float32."""
-        gate_up = linear(x, self.w_gate_up, out_dtype=ctx.dtype)
         act = torch.empty((x.shape[0], self.inter), dtype=ctx.dtype, device=x.device)
-        kernels.gated_act(gate_up, act, self.activation)
+        if kernels.skinny_ok(x, self.w_gate_up):
+            # few tokens: both products and the activation in one pass over the weights
+            kernels.skinny_gemm(x, self.w_gate_up, act, "gated", self.activation)
+        else:
+            gate_up = linear(x, self.w_gate_up, out_dtype=ctx.dtype)
+            kernels.gated_act(gate_up, act, self.activation)
         return linear(act, self.w_down, out_dtype=torch.float32)
 
 

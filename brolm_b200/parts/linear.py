@@ -3,8 +3,10 @@
 element type in the same way).
 
 * float32 weight: the framework's own CUDA-core kernel, true 32-bit.
-* bfloat16 weight: the library product (cuBLAS through torch), float32
-  accumulation; the result is bfloat16 or, on request, float32.
+* bfloat16 weight, up to 16 rows (decode steps): the framework's own
+  weight-streaming tensor-core kernel, float32 accumulation.
+* bfloat16 weight, more rows: the library product (cuBLAS through torch),
+  float32 accumulation.  The result is bfloat16 or, on request, float32.
 """
 from __future__ import annotations
 
@@ -35,6 +37,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         if x.dtype != torch.bfloat16:
             x = x.to(torch.bfloat16)
         want = out_dtype or torch.bfloat16
+        if kernels.skinny_ok(x, weight) and want in (torch.bfloat16, torch.float32):
+            y = out if out is not None else torch.empty((M, N), dtype=want, device=x.device)
+            kernels.skinny_gemm(x, weight, y)
+            return y
         if want == torch.bfloat16:
             return torch.mm(x, weight.t(), out=out) if out is not None else torch.mm(x, weight.t())
         if out is not None:

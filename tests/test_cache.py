@@ -119,3 +119,20 @@ def test_slots_come_back_and_state_starts_at_zero():
     with pytest.raises(CacheFull):
         for _ in range(3):
             c.alloc_slot()
+
+
+def test_write_rows_follow_the_pages_and_skip_what_the_ring_drops():
+    c = Cache([KVSpec(1, 16, None), KVSpec(1, 16, 100)], max_tokens=1024, dtype=torch.float32, device="cpu")
+    full, win = c.kv_groups
+    a, b = c.alloc_slot(), c.alloc_slot()
+    c.reserve({a: 300, b: 3})
+    rows = c.write_rows(0, [a, b], [0, 0], [300, 3])
+    assert rows.shape == (303,) and rows[0] == full.pages[a][0] * 64 and rows[299] == full.pages[a][4] * 64 + 43
+    assert rows[300] == full.pages[b][0] * 64
+    rows = c.write_rows(1, [a, b], [0, 0], [300, 3])                 # ring of 128: the first 172 are dropped
+    assert (rows[:172] == -1).all() and (rows[172:300] >= 0).all() and len(set(rows[172:300].tolist())) == 128
+    assert rows[172] == win.pages[a][(172 % 128) // 64] * 64 + 172 % 64
+    c.commit({a: 300, b: 3})
+    c.reserve({a: 301, b: 4})
+    rows = c.write_rows(1, [a, -1, b], [300, 0, 3], [301, 1, 4])       # a decode step with a padding row
+    assert rows.tolist() == [win.pages[a][(300 % 128) // 64] * 64 + 300 % 64, -1, win.pages[b][0] * 64 + 3]

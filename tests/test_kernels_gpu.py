@@ -120,6 +120,51 @@ def test_linear_f32_strided_views():
     assert float(out[:, :8].abs().max()) == 0 and float(out[:, 28:].abs().max()) == 0
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(16, 64), (40, 72), (1000, 200), (2304, 2304), (48, 9216)])
+def test_skinny_gemm(M, N, K):
+    g = torch.Generator().manual_seed(M * 1000 + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    ref = plain.linear(x, w)
+    for dt in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N), 7.0, dtype=dt, device=DEV)
+        kernels.skinny_gemm(x.to(DEV), w.to(DEV), out)
+        close(out, ref, torch.float32 if dt == torch.float32 else torch.bfloat16,
+              scale=float(ref.abs().max()) * (50 if dt == torch.float32 else 1))
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    kernels.skinny_gemm(x.to(DEV), w.to(DEV), out, "softcap", cap=3.0)
+    close(out, plain.soft_cap(ref, 3.0), torch.float32, scale=3.0 * 50)
+    # a row gives the same bits alone and in the batch
+    one = torch.empty(1, N, dtype=torch.float32, device=DEV)
+    kernels.skinny_gemm(x[M - 1:M].to(DEV), w.to(DEV), one, "softcap", cap=3.0)
+    assert torch.equal(one[0], out[M - 1])
+
+
+@pytest.mark.parametrize("M,F,K,act", [(1, 16, 64, "gelu_tanh"), (8, 328, 96, "silu"), (13, 9216, 128, "gelu_tanh"),
+                                       (16, 40, 2304, "gelu_tanh")])
+def test_skinny_gemm_gated(M, F, K, act):
+    g = torch.Generator().manual_seed(F + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * F, K, generator=g) * 0.1).to(torch.bfloat16)
+    gate, up = plain.linear(x, w[:F]), plain.linear(x, w[F:])
+    ref = (plain.gelu_tanh(gate) if act == "gelu_tanh" else gate * torch.sigmoid(gate)) * up
+    out = torch.empty(M, F, dtype=torch.bfloat16, device=DEV)
+    kernels.skinny_gemm(x.to(DEV), w.to(DEV), out, "gated", act)
+    close(out, ref, torch.bfloat16)
+
+
+def test_skinny_gemm_strided_input():
+    g = torch.Generator().manual_seed(1)
+    big = torch.randn(5, 3 * 64, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(24, 64, generator=g).to(torch.bfloat16).to(DEV)
+    x = big[:, 64:128]
+    assert kernels.skinny_ok(x, w) and not kernels.skinny_ok(big[:, 1:65], w)
+    out = torch.empty(5, 24, dtype=torch.float32, device=DEV)
+    kernels.skinny_gemm(x, w, out)
+    close(out, plain.linear(x.cpu(), w.cpu()), torch.float32, scale=float(out.abs().max()) * 50)
+
+
 def _rope_case(dtype, n_q, n_kv, hd, ring, page, lengths, seed):
     """Prompt pass of unequal sequences: rotation against the oracle and the pages written."""
     g = torch.Generator().manual_seed(seed)
@@ -128,7 +173,6 @@ def _rope_case(dtype, n_q, n_kv, hd, ring, page, lengths, seed):
     width = (n_q + 2 * n_kv) * hd
     qkv = torch.randn(T, width, generator=g).to(dtype)
     positions = torch.cat([torch.arange(n) for n in lengths]).int()
-    tok_seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lengths)]).int()
     theta = 1000.0
     half = hd // 2
     inv = torch.tensor(theta, dtype=torch.float64) ** (-2.0 * torch.arange(half, dtype=torch.float64) / hd)
@@ -145,8 +189,13 @@ def _rope_case(dtype, n_q, n_kv, hd, ring, page, lengths, seed):
     kp = torch.zeros(n_pages, n_kv, page, hd, dtype=dtype, device=DEV)
     vp = torch.zeros_like(kp)
     dq = qkv.clone().to(DEV)
-    kernels.rope_kv_write(dq, positions.to(DEV), tok_seq.to(DEV), table.to(DEV), n_q, n_kv, hd, hd, kp, vp,
-                          pt.to(DEV), torch.tensor(lengths, dtype=torch.int32, device=DEV), ring, page)
+    rows = []
+    for b, n in enumerate(lengths):
+        for p_ in range(n):
+            ridx = p_ % ring
+            rows.append(int(pt[b, ridx // page]) * page + ridx % page if p_ >= n - ring else -1)
+    kernels.rope_kv_write(dq, positions.to(DEV), table.to(DEV), n_q, n_kv, hd, hd, kp, vp,
+                          torch.tensor(rows, dtype=torch.int32, device=DEV), page)
     q_ref = plain.rope(qkv[:, :n_q * hd], positions, hd, theta)
     k_ref = plain.rope(qkv[:, n_q * hd:(n_q + n_kv) * hd], positions, hd, theta)
     close(dq[:, :n_q * hd], q_ref, dtype)
@@ -181,7 +230,7 @@ def test_rope_skips_padding_rows():
     table = torch.zeros(8, 8, 2)
     table[..., 1] = 1.0   # a quarter turn everywhere
     pos = torch.tensor([-1, 2, -1, 3], dtype=torch.int32, device=DEV)
-    kernels.rope_kv_write(qkv, pos, None, table.to(DEV), 2, 1, 16, 16, None, None, None, None, 64, 64)
+    kernels.rope_kv_write(qkv, pos, table.to(DEV), 2, 1, 16, 16)
     assert torch.equal(qkv[0], before[0]) and torch.equal(qkv[2], before[2])
     assert not torch.equal(qkv[1, :48], before[1, :48])
 

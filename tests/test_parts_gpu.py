@@ -37,7 +37,9 @@ def make_ctx(cache, mode, lengths_before, n_new, dtype):
         positions=i32([p for a, n in zip(lengths_before, n_new) for p in range(a, a + n)]),
         tok_seq=i32([i for i, n in enumerate(n_new) for _ in range(n)]), cu_q=i32(cu), kv_len=i32(new_len),
         slots_dev=i32(slots), max_q_len=max(n_new),
-        page_tables=[cache.page_table(g, slots).to(DEV) for g in range(len(cache.kv_groups))], host_lengths=new_len)
+        page_tables=[cache.page_table(g, slots).to(DEV) for g in range(len(cache.kv_groups))],
+        cache_rows=[i32(cache.write_rows(g, slots, lengths_before, new_len).tolist())
+                    for g in range(len(cache.kv_groups))], host_lengths=new_len)
 
 
 def test_rmsnorm_part():
