@@ -508,24 +508,33 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
 }
 
 // Merge the splits of one (sequence, head): out = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m).
-__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    bf16* __restrict__ out, const int32_t* __restrict__ cu_q, int out_stride, int n_q,
-                                    int n_splits, int hd) {
+// The statistics of all splits are fetched at once (one per thread) and the
+// factors go to shared memory, so the loop over the partial outputs has no
+// dependent loads.
+__global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restrict__ part_o,
+                                                           const float* __restrict__ part_ml, bf16* __restrict__ out,
+                                                           const int32_t* __restrict__ cu_q, int out_stride, int n_q,
+                                                           int n_splits, int hd) {
+    extern __shared__ float factor[];                 // [n_splits], then scratch for the block reductions
+    float* scratch = factor + n_splits;
     const int head = blockIdx.x, b = blockIdx.y;
     const size_t slot0 = ((size_t)b * n_q + head) * n_splits;
     float mx = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, part_ml[(slot0 + s) * 2]);
+    for (int s = threadIdx.x; s < n_splits; s += blockDim.x) mx = fmaxf(mx, part_ml[(slot0 + s) * 2]);
+    mx = block_max(mx, scratch);
+    float sum = 0.0f;
+    for (int s = threadIdx.x; s < n_splits; s += blockDim.x) {
+        const float f = mx > -INFINITY ? fast_exp2(part_ml[(slot0 + s) * 2] - mx) : 0.0f;
+        factor[s] = f;
+        sum += part_ml[(slot0 + s) * 2 + 1] * f;
+    }
+    sum = block_sum(sum, scratch);                    // also makes factor[] visible to every thread
+    const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float sum = 0.0f, acc = 0.0f;
-        if (mx > -INFINITY) {
+        float acc = 0.0f;
 #pragma unroll 8
-            for (int s = 0; s < n_splits; ++s) {
-                const float f = fast_exp2(part_ml[(slot0 + s) * 2] - mx);
-                sum += part_ml[(slot0 + s) * 2 + 1] * f;
-                acc += part_o[(slot0 + s) * hd + d] * f;
-            }
-        }
-        out[(size_t)cu_q[b] * out_stride + head * hd + d] = __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
+        for (int s = 0; s < n_splits; ++s) acc += part_o[(slot0 + s) * hd + d] * factor[s];
+        out[(size_t)cu_q[b] * out_stride + head * hd + d] = __float2bfloat16_rn(acc * inv);
     }
 }
 
@@ -559,7 +568,7 @@ int launch_decode(const MmaArgs& a, int batch, cudaStream_t stream) {
     int st = launch_status();
     if (st != 0 || a.n_splits == 1) return st;
     dim3 cgrid(a.n_kv * a.group, batch);
-    attn_combine_kernel<<<cgrid, 128, 0, stream>>>(a.part_o, a.part_ml, a.out, a.cu_q, a.out_stride, a.n_kv * a.group,
+    attn_combine_kernel<<<cgrid, 128, (a.n_splits + 33) * sizeof(float), stream>>>(a.part_o, a.part_ml, a.out, a.cu_q, a.out_stride, a.n_kv * a.group,
                                                    a.n_splits, a.hd);
     return launch_status();
 }
@@ -608,7 +617,7 @@ BROLM_API int brolm_attn_decode_mma(const void* q, int q_stride, void* out, int 
     int st = check_common(hd, group, n_kv, q_stride, out_stride, batch);
     if (st) return st;
     if (group > 16) return BROLM_ERR_TOO_LARGE;
-    if (page_size != KT || ring <= 0 || ring % KT != 0 || n_splits < 1 || n_splits > 65535) return BROLM_ERR_BAD_SIZE;
+    if (page_size != KT || ring <= 0 || ring % KT != 0 || n_splits < 1 || n_splits > 4096) return BROLM_ERR_BAD_SIZE;
     if (n_splits > 1 && (!part_o || !part_ml)) return BROLM_ERR_BAD_SIZE;
     if (((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15)) return BROLM_ERR_ALIGNMENT;
     MmaArgs a = {};

@@ -159,8 +159,11 @@ BROLM_API int brolm_rmsnorm(const void* x, int x_dtype, const void* rows, const 
 //     out = rmsnorm(h; w_next)   if w_next        (src/gemma2.cpp:376, :349 of the next layer)
 // h is the float residual stream.  Same register scheme as above.
 // ---------------------------------------------------------------------------
+// y may come as n_parts partial sums, part_stride elements apart (the slices
+// of a product that was cut along K); they are added in order while loading.
 template <typename Y, typename W, typename O, int MAXC>
 __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict__ h, const Y* __restrict__ y,
+                                                               int n_parts, long long part_stride,
                                                                const W* __restrict__ w_post, float eps_post,
                                                                float off_post, const W* __restrict__ w_next,
                                                                float eps_next, float off_next, O* __restrict__ out,
@@ -171,11 +174,16 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
     const Y* yr = y + (size_t)r * hidden;
     O* dst = out + (size_t)r * hidden;
     if (MAXC == 0) {
+        auto y_at = [&](int i) {
+            float v = to_float(yr[i]);
+            for (int s = 1; s < n_parts; ++s) v += to_float(yr[(size_t)s * part_stride + i]);
+            return v;
+        };
         float inv_post = 1.0f;
         if (w_post) {
             float ss = 0.0f;
             for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-                const float v = to_float(yr[i]);
+                const float v = y_at(i);
                 ss += v * v;
             }
             ss = block_sum(ss, scratch);
@@ -183,7 +191,7 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
         }
         float ss2 = 0.0f;
         for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-            float v = to_float(yr[i]);
+            float v = y_at(i);
             if (w_post) v = v * inv_post * (off_post + to_float(w_post[i]));
             const float s = hr[i] + v;
             hr[i] = s;
@@ -206,6 +214,12 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
         for (int e = 0; e < 4; ++e) v[c][e] = res[c][e] = gp[c][e] = gn[c][e] = 0.0f;
         if (i < hidden) {
             load4(yr + i, v[c]);
+            for (int s = 1; s < n_parts; ++s) {
+                float t[4];
+                load4(yr + (size_t)s * part_stride + i, t);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[c][e] += t[e];
+            }
             load4(hr + i, res[c]);
             if (w_post) load4(w_post + i, gp[c]);
             if (w_next) load4(w_next + i, gn[c]);
@@ -249,12 +263,12 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
 }
 
 template <typename Y, typename W, typename O>
-static int residual_launch(void* h, const void* y, const void* w_post, float eps_post, float off_post,
+static int residual_launch(void* h, const void* y, int n_parts, long long part_stride, const void* w_post, float eps_post, float off_post,
                            const void* w_next, float eps_next, float off_next, void* out, int n, int hidden,
                            cudaStream_t s) {
     int c = vec_chunks(hidden, h, y, w_post, w_next);
-    if (c && ((uintptr_t)out & 15)) c = 0;
-#define BROLM_RES(C) residual_rmsnorm_kernel<Y, W, O, C><<<n, 256, 0, s>>>((float*)h, (const Y*)y, (const W*)w_post, \
+    if (c && (((uintptr_t)out & 15) || part_stride % 4 != 0)) c = 0;
+#define BROLM_RES(C) residual_rmsnorm_kernel<Y, W, O, C><<<n, 256, 0, s>>>((float*)h, (const Y*)y, n_parts, part_stride, (const W*)w_post, \
         eps_post, off_post, (const W*)w_next, eps_next, off_next, (O*)out, hidden)
     if (c == 1) BROLM_RES(1); else if (c == 4) BROLM_RES(4); else if (c == 8) BROLM_RES(8); else BROLM_RES(0);
 #undef BROLM_RES
@@ -262,33 +276,35 @@ static int residual_launch(void* h, const void* y, const void* w_post, float eps
 }
 
 template <typename Y, typename W>
-static int residual_out(void* h, const void* y, const void* w_post, float eps_post, float off_post,
+static int residual_out(void* h, const void* y, int n_parts, long long part_stride, const void* w_post, float eps_post, float off_post,
                         const void* w_next, float eps_next, float off_next, void* out, int out_dtype, int n,
                         int hidden, cudaStream_t s) {
     if (out_dtype == BROLM_F32)
-        return residual_launch<Y, W, float>(h, y, w_post, eps_post, off_post, w_next, eps_next, off_next, out, n, hidden, s);
+        return residual_launch<Y, W, float>(h, y, n_parts, part_stride, w_post, eps_post, off_post, w_next, eps_next, off_next, out, n, hidden, s);
     if (out_dtype == BROLM_BF16)
-        return residual_launch<Y, W, bf16>(h, y, w_post, eps_post, off_post, w_next, eps_next, off_next, out, n, hidden, s);
+        return residual_launch<Y, W, bf16>(h, y, n_parts, part_stride, w_post, eps_post, off_post, w_next, eps_next, off_next, out, n, hidden, s);
     return BROLM_ERR_BAD_DTYPE;
 }
 
 // w_post and w_next share one element type (w_dtype); either may be null.
-BROLM_API int brolm_residual_rmsnorm(void* h, const void* y, int y_dtype, const void* w_post, float eps_post,
+BROLM_API int brolm_residual_rmsnorm(void* h, const void* y, int y_dtype, int n_parts, long long part_stride,
+                                     const void* w_post, float eps_post,
                                      float off_post, const void* w_next, float eps_next, float off_next,
                                      int w_dtype, void* out, int out_dtype, int n, int hidden,
                                      cudaStream_t stream) {
     if (n <= 0) return BROLM_OK;
+    if (n_parts < 1) return BROLM_ERR_BAD_SIZE;
     if (y_dtype == BROLM_F32 && w_dtype == BROLM_F32)
-        return residual_out<float, float>(h, y, w_post, eps_post, off_post, w_next, eps_next, off_next, out,
+        return residual_out<float, float>(h, y, n_parts, part_stride, w_post, eps_post, off_post, w_next, eps_next, off_next, out,
                                           out_dtype, n, hidden, stream);
     if (y_dtype == BROLM_F32 && w_dtype == BROLM_BF16)
-        return residual_out<float, bf16>(h, y, w_post, eps_post, off_post, w_next, eps_next, off_next, out,
+        return residual_out<float, bf16>(h, y, n_parts, part_stride, w_post, eps_post, off_post, w_next, eps_next, off_next, out,
                                          out_dtype, n, hidden, stream);
     if (y_dtype == BROLM_BF16 && w_dtype == BROLM_F32)
-        return residual_out<bf16, float>(h, y, w_post, eps_post, off_post, w_next, eps_next, off_next, out,
+        return residual_out<bf16, float>(h, y, n_parts, part_stride, w_post, eps_post, off_post, w_next, eps_next, off_next, out,
                                          out_dtype, n, hidden, stream);
     if (y_dtype == BROLM_BF16 && w_dtype == BROLM_BF16)
-        return residual_out<bf16, bf16>(h, y, w_post, eps_post, off_post, w_next, eps_next, off_next, out,
+        return residual_out<bf16, bf16>(h, y, n_parts, part_stride, w_post, eps_post, off_post, w_next, eps_next, off_next, out,
                                         out_dtype, n, hidden, stream);
     return BROLM_ERR_BAD_DTYPE;
 }

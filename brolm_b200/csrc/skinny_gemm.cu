@@ -62,6 +62,8 @@ struct SkinnyArgs {
     int out_f32;
     int act;
     float cap;
+    int ksplit;           // blocks along K; > 1: block (x, s) writes float partial sums to y + s * part_stride
+    long long part_stride;
 };
 
 // MT: 16-row tiles of W per block.  NT: 8-token tiles.
@@ -87,7 +89,9 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.0f;
 
-    const int nkb = (a.K + KB - 1) / KB;
+    const int nkb_all = (a.K + KB - 1) / KB;
+    const int per = (nkb_all + a.ksplit - 1) / a.ksplit;
+    const int kb_first = blockIdx.y * per, nkb = min(nkb_all, kb_first + per);
     uint4 wc[2][MT][2], xc[2][NT];                                 // [half of the block][tile][row r / r + 8]
 
     auto load = [&](int kb, uint4 (&wv)[2][MT][2], uint4 (&xv)[2][NT]) {
@@ -110,7 +114,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
     };
     (void)w_rows;
 
-    int kb = warp;
+    int kb = kb_first + warp;
     if (kb < nkb) load(kb, wc, xc);
     for (; kb < nkb; kb += WARPS) {
         uint4 wn[2][MT][2], xn[2][NT];
@@ -168,7 +172,8 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
             if (EPI == EPI_SOFTCAP) v = soft_cap(v, a.cap);
         }
         if (col < n_limit && tok < a.M) {
-            if (a.out_f32) reinterpret_cast<float*>(a.y)[(size_t)tok * a.ldy + col] = v;
+            if (a.ksplit > 1) reinterpret_cast<float*>(a.y)[blockIdx.y * a.part_stride + (size_t)tok * a.ldy + col] = v;
+            else if (a.out_f32) reinterpret_cast<float*>(a.y)[(size_t)tok * a.ldy + col] = v;
             else reinterpret_cast<bf16*>(a.y)[(size_t)tok * a.ldy + col] = __float2bfloat16_rn(v);
         }
     }
@@ -177,7 +182,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
 template <int MT, int NT, int EPI>
 int launch(const SkinnyArgs& a, cudaStream_t stream) {
     constexpr int cols = (EPI == EPI_GATED ? MT / 2 : MT) * 16;
-    const int blocks = (a.N + cols - 1) / cols;
+    dim3 blocks((a.N + cols - 1) / cols, a.ksplit);
     skinny_kernel<MT, NT, EPI><<<blocks, WARPS * 32, 0, stream>>>(a);
     return launch_status();
 }
@@ -198,8 +203,11 @@ int dispatch(const SkinnyArgs& a, int mt, cudaStream_t stream) {
 // epilogue 0: Y = X W^T (bfloat16, or float when out_f32); 1: Y = act(X Wg^T) * (X Wu^T) with
 // W = [Wg; Wu] of 2N rows; 2: Y = cap * tanh(X W^T / cap), float.  M <= 16; K a multiple of 8;
 // rows of X and W 16-byte aligned.  tiles: 16-row tiles of W per block (1, 2 or 4).
+// ksplit > 1 (epilogue 0 only): K is cut into ksplit slices, slice s writes its float partial
+// sums at y + s * part_stride (elements); the reader adds the slices in order.
 BROLM_API int brolm_skinny_gemm(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int M, int N, int K,
-                                int epilogue, int out_f32, int act, float cap, int tiles, cudaStream_t stream) {
+                                int epilogue, int out_f32, int act, float cap, int tiles, int ksplit,
+                                long long part_stride, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return BROLM_OK;
     if (M > 16) return BROLM_ERR_TOO_LARGE;
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return BROLM_ERR_ALIGNMENT;
@@ -208,6 +216,8 @@ BROLM_API int brolm_skinny_gemm(const void* x, int ldx, const void* w, int ldw, 
     SkinnyArgs a;
     a.x = (const bf16*)x; a.w = (const bf16*)w; a.y = y; a.ldx = ldx; a.ldw = ldw; a.ldy = ldy;
     a.M = M; a.N = N; a.K = K; a.out_f32 = out_f32; a.act = act; a.cap = cap;
+    if (ksplit < 1 || ksplit > 64 || (ksplit > 1 && epilogue != EPI_STORE)) return BROLM_ERR_BAD_SIZE;
+    a.ksplit = ksplit; a.part_stride = part_stride;
     if (epilogue == EPI_STORE) return dispatch<EPI_STORE>(a, tiles, stream);
     if (epilogue == EPI_GATED) return dispatch<EPI_GATED>(a, tiles, stream);
     if (epilogue == EPI_SOFTCAP) { a.out_f32 = 1; return dispatch<EPI_SOFTCAP>(a, tiles, stream); }

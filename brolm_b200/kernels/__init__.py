@@ -108,8 +108,11 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float, ou
 def residual_rmsnorm(h: torch.Tensor, y: torch.Tensor, post_weight: Optional[torch.Tensor], post_eps: float,
                      post_offset: float, next_weight: Optional[torch.Tensor], next_eps: float, next_offset: float,
                      out: Optional[torch.Tensor]) -> None:
-    """h += rmsnorm(y; post) (or y when post_weight is None); out = rmsnorm(h; next) when next_weight is given."""
-    assert h.dtype == torch.float32 and h.is_contiguous() and y.is_contiguous() and y.shape == h.shape
+    """h += rmsnorm(y; post) (or y when post_weight is None); out = rmsnorm(h; next) when next_weight is given.
+
+    ``y`` may be [parts, rows, hidden]: partial sums that are added in order first."""
+    assert h.dtype == torch.float32 and h.is_contiguous() and y.is_contiguous() and tuple(y.shape[-2:]) == tuple(h.shape)
+    n_parts, part_stride = (y.shape[0], y.stride(0)) if y.dim() == 3 else (1, 0)
     wd = None
     for w in (post_weight, next_weight):
         if w is not None:
@@ -119,9 +122,10 @@ def residual_rmsnorm(h: torch.Tensor, y: torch.Tensor, post_weight: Optional[tor
             wd = w.dtype
     if next_weight is not None:
         assert out is not None and out.is_contiguous() and out.shape == h.shape
-    f = _fn("core", "brolm_residual_rmsnorm", [c_void_p, c_void_p, c_int, c_void_p, c_float, c_float, c_void_p,
-                                               c_float, c_float, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(h), _ptr(y), _code(y), _ptr(post_weight), post_eps, post_offset, _ptr(next_weight), next_eps,
+    f = _fn("core", "brolm_residual_rmsnorm", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_float, c_float,
+                                               c_void_p, c_float, c_float, c_int, c_void_p, c_int, c_int, c_int,
+                                               c_void_p])
+    _check(f(_ptr(h), _ptr(y), _code(y), n_parts, part_stride, _ptr(post_weight), post_eps, post_offset, _ptr(next_weight), next_eps,
              next_offset, _CODES[wd] if wd is not None else F32, _ptr(out) if next_weight is not None else None,
              _code(out) if next_weight is not None else F32, h.shape[0], h.shape[-1], _stream()),
            "residual_rmsnorm")
@@ -194,6 +198,15 @@ def skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
             x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
+def skinny_parts(x: torch.Tensor, weight: torch.Tensor, sms: int = 148) -> int:
+    """Into how many slices of K a few-token product is cut so that enough blocks
+    stream the weights at once (about three per SM, two passes per warp at least)."""
+    blocks = (weight.shape[0] + 15) // 16
+    kblocks = (x.shape[1] + 63) // 64
+    want = (3 * sms + blocks - 1) // blocks
+    return max(1, min(want, kblocks // 16, 8))
+
+
 def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "store",
                 activation: str = "gelu_tanh", cap: float = 0.0) -> None:
     """out = x @ weight^T for at most 16 rows of x (bfloat16 in, float32 accumulation).
@@ -201,25 +214,30 @@ def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilog
     ``epilogue``: "store" (out bfloat16 or float32), "gated" (weight = [Wg; Wu],
     out = act(x Wg^T) * (x Wu^T)), "softcap" (out float32 = cap * tanh(. / cap)).
     """
-    assert skinny_ok(x, weight) and out.stride(1) == 1 and out.shape[0] == x.shape[0]
+    assert skinny_ok(x, weight) and out.stride(-1) == 1 and out.shape[-2] == x.shape[0]
     M, K = x.shape
     assert weight.shape[1] == K
     code = {"store": 0, "gated": 1, "softcap": 2}[epilogue]
-    N = out.shape[1]
+    N = out.shape[-1]
+    ksplit, part_stride = 1, 0
+    if out.dim() == 3:                      # [parts, M, N] float32 partial sums along K
+        assert code == 0 and out.dtype == torch.float32 and out.stride(1) == N
+        ksplit, part_stride = out.shape[0], out.stride(0)
     assert weight.shape[0] == (2 * N if code == 1 else N)
     if code == 1:
         if activation not in ACTIVATIONS:
             raise KernelError(f"skinny_gemm: unknown activation '{activation}'")
         tiles = 4 if N >= 32 * 296 else 2
     else:
-        tiles = 4 if N >= 64 * 296 else 2 if N >= 32 * 296 else 1
+        tiles = 2 if N >= 32 * 296 else 1
     if code == 2:
         assert out.dtype == torch.float32
     f = _fn("skinny_gemm", "brolm_skinny_gemm", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-                                                 c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
-    _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K, code,
-             1 if out.dtype == torch.float32 else 0, ACTIVATIONS.get(activation, 0), cap, tiles, _stream()),
-           "skinny_gemm")
+                                                 c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_longlong,
+                                                 c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(-2), M, N, K, code,
+             1 if out.dtype == torch.float32 else 0, ACTIVATIONS.get(activation, 0), cap, tiles, ksplit, part_stride,
+             _stream()), "skinny_gemm")
 
 
 def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor, *, n_kv: int,
@@ -321,5 +339,5 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
 
 
 __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "embed_scale", "rmsnorm", "residual_rmsnorm",
-           "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_ok", "attention_simt", "attention_prefill_mma", "attention_decode_mma",
+           "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_ok", "skinny_parts", "attention_simt", "attention_prefill_mma", "attention_decode_mma",
            "decode_splits", "argmax", "sample"]

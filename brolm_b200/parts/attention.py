@@ -58,7 +58,8 @@ class Attention(Part):
             self.position.prepare(max_positions, device)
 
     def forward(self, x: torch.Tensor, ctx, entry, writes_cache: bool = True) -> torch.Tensor:
-        """x (tokens, hidden) in the step's element type -> (tokens, hidden) float32."""
+        """x (tokens, hidden) in the step's element type -> (tokens, hidden) float32, or
+        [parts, tokens, hidden] partial sums that the residual kernel adds."""
         qkv = linear(x, self.w_qkv, out_dtype=ctx.dtype)
         k_pages, v_pages, table, ring, page = ctx.kv(entry)
         rot = self.position.rotary_dim if self.position is not None else 0
@@ -82,7 +83,7 @@ class Attention(Part):
                 raise NotImplementedError("a layer that reads another layer's windowed cache cannot take a "
                                           "prompt longer than the ring in one step")
             self.attend_paged(q, out, ctx, common, k_pages, v_pages, table, ring, page)
-        return linear(out, self.w_o, out_dtype=torch.float32)
+        return linear(out, self.w_o, out_dtype=torch.float32, parts_ok=True)
 
     # bfloat16 runs on the tensor cores when the sizes allow; everything else, and
     # all of float32, takes the exact CUDA-core kernel

@@ -41,7 +41,7 @@ class GatedFeedForward(Part):
         else:
             gate_up = linear(x, self.w_gate_up, out_dtype=ctx.dtype)
             kernels.gated_act(gate_up, act, self.activation)
-        return linear(act, self.w_down, out_dtype=torch.float32)
+        return linear(act, self.w_down, out_dtype=torch.float32, parts_ok=True)
 
 
 register_part("feedforward", "gated", GatedFeedForward)

@@ -18,7 +18,10 @@ from .. import kernels
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+           out: Optional[torch.Tensor] = None, parts_ok: bool = False) -> torch.Tensor:
+    """``parts_ok``: the caller adds partial sums itself (the residual kernel
+    does); the result may then be [parts, M, N] float32, the slices of a
+    product that was cut along K so that more blocks stream the weights."""
     M = x.shape[0]
     N = weight.shape[0]
     if weight.dtype == torch.float32:
@@ -38,6 +41,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
             x = x.to(torch.bfloat16)
         want = out_dtype or torch.bfloat16
         if kernels.skinny_ok(x, weight) and want in (torch.bfloat16, torch.float32):
+            parts = kernels.skinny_parts(x, weight) if (parts_ok and want == torch.float32 and out is None) else 1
+            if parts > 1:
+                y = torch.empty((parts, M, N), dtype=torch.float32, device=x.device)
+                kernels.skinny_gemm(x, weight, y)
+                return y
             y = out if out is not None else torch.empty((M, N), dtype=want, device=x.device)
             kernels.skinny_gemm(x, weight, y)
             return y

@@ -52,6 +52,8 @@ def add_then_norm(h: torch.Tensor, y: torch.Tensor, post: Optional[Part], nxt: O
     fused_next = nxt is None or isinstance(nxt, RMSNorm)
     if fused_post and fused_next and post is not None and nxt is not None and post.weight.dtype != nxt.weight.dtype:
         fused_next = False
+    if y.dim() == 3 and not fused_post:
+        y = y.sum(dim=0)                       # partial sums, and a norm that wants the whole
     if not fused_post:
         y = post.apply(y, torch.float32)
         post = None

@@ -154,6 +154,28 @@ def test_skinny_gemm_gated(M, F, K, act):
     close(out, ref, torch.bfloat16)
 
 
+@pytest.mark.parametrize("parts", [2, 3, 8])
+def test_skinny_gemm_partial_sums_feed_the_residual_kernel(parts):
+    g = torch.Generator().manual_seed(parts)
+    M, N, K = 5, 328, 9216
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    y = torch.full((parts, M, N), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.skinny_gemm(x.to(DEV), w.to(DEV), y)
+    ref = plain.linear(x, w)
+    close(y.sum(0), ref, torch.float32, scale=float(ref.abs().max()) * 50)
+    h = torch.randn(M, N, generator=g)
+    gain = (torch.randn(N, generator=g) * 0.1).to(torch.bfloat16)
+    hd_ = h.clone().to(DEV)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    kernels.residual_rmsnorm(hd_, y, gain.to(DEV), 1e-6, 1.0, gain.to(DEV), 1e-6, 1.0, out)
+    h_ref = h.double() + plain.rms_norm(ref, gain, 1e-6)
+    close(hd_, h_ref, torch.float32, scale=float(h_ref.abs().max()) * 50)
+    close(out, plain.rms_norm(h_ref, gain, 1e-6), torch.bfloat16)
+    assert kernels.skinny_parts(torch.empty(8, 9216), torch.empty(2304, 9216)) == 4
+    assert kernels.skinny_parts(torch.empty(8, 2304), torch.empty(18432, 2304)) == 1
+
+
 def test_skinny_gemm_strided_input():
     g = torch.Generator().manual_seed(1)
     big = torch.randn(5, 3 * 64, generator=g).to(torch.bfloat16).to(DEV)
