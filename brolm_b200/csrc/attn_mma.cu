@@ -99,6 +99,7 @@ struct MmaArgs {
     int n_kv, group, hd;
     float scale, cap;
     int window;
+    int sms;                // SMs of the device (prompt kernel: pairing of heavy and light tiles)
     // split-KV scratch
     int n_splits;
     float* part_o;          // [B][n_q][n_splits][hd]
@@ -127,10 +128,20 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
     bf16* Vs = Ks + KT * hd;
     const uint32_t qs_base = smem_u32(Qs), ks_base = smem_u32(Ks), vs_base = smem_u32(Vs);
 
-    const int b = blockIdx.z, g = blockIdx.y;
+    // Which (row tile, kv head, sequence) this block takes.  A causal row tile
+    // costs as many key tiles as its index, so blocks are handed out heaviest
+    // first; and when all blocks fit on the device at once (at most two per
+    // SM), the blocks after the first `sms` take the lightest tiles in rising
+    // order, so that an SM that got the k-th heaviest tile gets the k-th
+    // lightest next to it and all SMs finish together.
+    const int per_x = gridDim.y * gridDim.z, total = gridDim.x * per_x;
+    const int n = blockIdx.x * per_x + blockIdx.z * gridDim.y + blockIdx.y;      // launch order
+    const int rank = (total <= 2 * a.sms && n >= a.sms) ? total - 1 - (n - a.sms) : n;
+    const int xt = gridDim.x - 1 - rank / per_x;                                // row tile, heaviest first
+    const int b = (rank % per_x) / gridDim.y, g = (rank % per_x) % gridDim.y;
     const int q0 = a.cu_q[b], q_len = a.cu_q[b + 1] - q0;
     const int n_rows = q_len * a.group;
-    const int row0 = blockIdx.x * BM;
+    const int row0 = xt * BM;
     if (row0 >= n_rows) return;
     const int rows_here = min(BM, n_rows - row0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -597,6 +608,13 @@ BROLM_API int brolm_attn_prefill_mma(const void* q, int q_stride, void* out, int
     a.q = (const bf16*)q; a.out = (bf16*)out; a.q_stride = q_stride; a.out_stride = out_stride;
     a.cu_q = (const int32_t*)cu_q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.kv_stride = kv_stride;
     a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window; a.n_splits = 1;
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    a.sms = sms;
     if (hd == 64) return launch_prefill<64, true>(a, batch, max_q_len, stream);
     if (hd == 128) return launch_prefill<128, true>(a, batch, max_q_len, stream);
     if (hd == 256) return launch_prefill<256, true>(a, batch, max_q_len, stream);

@@ -364,12 +364,70 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int32_t* __restr
     }
 }
 
+// bfloat16, rot == hd, hd a multiple of 16: eight pairs per thread with 16-byte
+// accesses; one block per token, items = heads * hd/16.
+__global__ void __launch_bounds__(256) rope_kv_write_vec_kernel(bf16* __restrict__ qkv,
+                                                                const int32_t* __restrict__ positions,
+                                                                const float2* __restrict__ cos_sin, int n_q, int n_kv,
+                                                                int hd, bf16* __restrict__ k_pages,
+                                                                bf16* __restrict__ v_pages,
+                                                                const int32_t* __restrict__ cache_rows,
+                                                                int page_size) {
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    if (pos < 0) return;
+    const int half = hd >> 1, per_head = half >> 3;
+    const int heads = n_q + 2 * n_kv;
+    const int crow = k_pages ? cache_rows[t] : -1;
+    bf16* row = qkv + (size_t)t * heads * hd;
+    for (int item = threadIdx.x; item < heads * per_head; item += blockDim.x) {
+        const int head = item / per_head, i0 = (item - head * per_head) << 3;
+        const bool is_v = head >= n_q + n_kv, is_k = !is_v && head >= n_q;
+        const bool rotate = !is_v && cos_sin != nullptr;
+        const bool keep = crow >= 0 && (is_k || is_v);
+        if (!rotate && !keep) continue;
+        bf16* p = row + (size_t)head * hd;
+        uint4 ra = *reinterpret_cast<const uint4*>(p + i0), rb = *reinterpret_cast<const uint4*>(p + half + i0);
+        if (rotate) {
+            const float4* cs = reinterpret_cast<const float4*>(cos_sin + (size_t)pos * half + i0);
+            __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&ra);
+            __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&rb);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 c = cs[j];                       // (cos, sin) of pairs 2j and 2j + 1
+                const float2 fa = __bfloat1622float2(a2[j]), fb = __bfloat1622float2(b2[j]);
+                a2[j] = __floats2bfloat162_rn(fa.x * c.x - fb.x * c.y, fa.y * c.z - fb.y * c.w);
+                b2[j] = __floats2bfloat162_rn(fa.x * c.y + fb.x * c.x, fa.y * c.w + fb.y * c.z);
+            }
+            *reinterpret_cast<uint4*>(p + i0) = ra;
+            *reinterpret_cast<uint4*>(p + half + i0) = rb;
+        }
+        if (keep) {
+            const int g = is_k ? head - n_q : head - n_q - n_kv;
+            bf16* dst = (is_k ? k_pages : v_pages) +
+                        (((size_t)(crow / page_size) * n_kv + g) * page_size + crow % page_size) * hd;
+            *reinterpret_cast<uint4*>(dst + i0) = ra;
+            *reinterpret_cast<uint4*>(dst + half + i0) = rb;
+        }
+    }
+}
+
 BROLM_API int brolm_rope_kv_write(void* qkv, int dtype, const void* positions, const void* cos_sin, int n_q, int n_kv,
                                   int hd, int rot, void* k_pages, void* v_pages, const void* cache_rows,
                                   int page_size, int tokens, cudaStream_t stream) {
     if (tokens <= 0) return BROLM_OK;
     if (rot > hd || (rot & 1) || (hd & 1) || page_size <= 0) return BROLM_ERR_BAD_SIZE;
     if (n_q + 2 * n_kv > 65535) return BROLM_ERR_TOO_LARGE;
+    if (dtype == BROLM_BF16 && (rot == hd || !cos_sin) && hd % 16 == 0 && ((uintptr_t)qkv & 15) == 0 &&
+        ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0 && ((uintptr_t)cos_sin & 15) == 0) {
+        int items = (n_q + 2 * n_kv) * (hd >> 4);
+        int th = (items + 31) / 32 * 32;
+        if (th > 256) th = 256;
+        rope_kv_write_vec_kernel<<<tokens, th, 0, stream>>>((bf16*)qkv, (const int32_t*)positions,
+                                                            (const float2*)cos_sin, n_q, n_kv, hd, (bf16*)k_pages,
+                                                            (bf16*)v_pages, (const int32_t*)cache_rows, page_size);
+        return launch_status();
+    }
     dim3 grid(tokens, n_q + 2 * n_kv);
     int threads = ((hd >> 1) + 31) / 32 * 32;
     if (threads > 256) threads = 256;
@@ -410,10 +468,36 @@ __global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ 
         o[j] = from_float<T>(act_apply(to_float(g[j]), act) * to_float(u[j]));
 }
 
+// bfloat16 with inter a multiple of 8: eight elements per thread, 16-byte accesses.
+__global__ void __launch_bounds__(256) gated_act_vec_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out,
+                                                            int inter, int act) {
+    const size_t t = blockIdx.x;
+    const bf16* g = gate_up + t * 2 * (size_t)inter;
+    const bf16* u = g + inter;
+    bf16* o = out + t * (size_t)inter;
+    for (int j = (blockIdx.y * blockDim.x + threadIdx.x) * 8; j < inter; j += gridDim.y * blockDim.x * 8) {
+        float gv[8], uv[8];
+        load8(g + j, gv);
+        load8(u + j, uv);
+        uint4 r;
+        __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            r2[e] = __floats2bfloat162_rn(act_apply(gv[2 * e], act) * uv[2 * e], act_apply(gv[2 * e + 1], act) * uv[2 * e + 1]);
+        *reinterpret_cast<uint4*>(o + j) = r;
+    }
+}
+
 BROLM_API int brolm_gated_act(const void* gate_up, void* out, int dtype, int tokens, int inter, int act,
                               cudaStream_t stream) {
     if (tokens <= 0) return BROLM_OK;
     if (act < 0 || act > 1) return BROLM_ERR_BAD_SIZE;
+    if (dtype == BROLM_BF16 && inter % 8 == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        int by = (inter / 8 + 255) / 256;
+        if (by > 65535) by = 65535;
+        gated_act_vec_kernel<<<dim3(tokens, by), 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, act);
+        return launch_status();
+    }
     int by = (inter + 1023) / 1024;
     if (by > 65535) by = 65535;
     dim3 grid(tokens, by);

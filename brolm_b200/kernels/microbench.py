@@ -83,6 +83,23 @@ def attn_prefill(args) -> None:
     print(f"attn_prefill tokens={T} window={args.window}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.1f} TFLOP/s")
 
 
+def model_prefill(args) -> None:
+    """One prompt through a model of Gemma 2 2B's layer sizes with few layers (for launch lists)."""
+    import brolm_b200 as bb
+    cfg = bb.Gemma2Config(num_hidden_layers=args.layers)
+    model = bb.Model(cfg, dtype="bfloat16", device=DEV).init_random(seed=0, on_device=True)
+    engine = bb.Engine(model, max_tokens=args.tokens + 64, max_slots=1)
+    prompt = torch.randint(0, cfg.vocab_size, (args.tokens,), generator=torch.Generator().manual_seed(1)).tolist()
+
+    def run():
+        (s,) = engine.open(1)
+        engine.step([s], [prompt])
+        engine.close([s])
+
+    ms = timed(run, args.reps)
+    print(f"model_prefill layers={args.layers} tokens={args.tokens}: {ms:.3f} ms")
+
+
 def norms(args) -> None:
     B, H = args.batch, args.hidden
     h = torch.randn(B, H, device=DEV)
@@ -98,7 +115,8 @@ def norms(args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "norms"])
+    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "model_prefill", "norms"])
+    ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -110,7 +128,8 @@ def main() -> None:
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--reps", type=int, default=20)
     args = ap.parse_args()
-    {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "norms": norms}[args.what](args)
+    {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "model_prefill": model_prefill,
+     "norms": norms}[args.what](args)
 
 
 if __name__ == "__main__":
