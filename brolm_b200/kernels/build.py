@@ -37,7 +37,7 @@ LIBRARIES: dict[str, list[str]] = {
     "skinny_gemm": ["skinny_gemm.cu"],
     "sampling": ["sampling.cu"],
 }
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "attn_mma.cuh"]
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
