@@ -35,9 +35,10 @@ LIBRARIES: dict[str, list[str]] = {
     "attn_simt": ["attn_simt.cu"],
     "attn_mma": ["attn_mma.cu"],
     "skinny_gemm": ["skinny_gemm.cu"],
+    "attn_noalloc": ["attn_decode_noalloc.cu"],
     "sampling": ["sampling.cu"],
 }
-HEADERS = ["common.cuh", "attn_mma.cuh"]
+HEADERS = ["common.cuh", "attn_mma.cuh", "attn_decode_noalloc.h"]
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
