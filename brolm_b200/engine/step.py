@@ -24,6 +24,7 @@ from typing import Optional, Sequence
 import numpy as np
 import torch
 
+from .. import kernels
 from ..cache import Cache, CacheError
 from .context import StepContext
 from .model import DecoderModel
@@ -164,6 +165,11 @@ class Engine:
         else:
             ctx, tok_dev, rows = self._context(plan)
             logits = self.model.forward(ctx, tok_dev, rows)
+            if plan.mode == "prefill" and self.model.dtype == torch.bfloat16 and self.device.type == "cuda":
+                code = kernels.gemm_tc_status(reset=True)      # waits for the step; 0 unless a bounded wait ran out
+                if code:
+                    raise StepError(f"step: a wait inside the tensor-core product kernel ran out (code {code}); "
+                                    f"the results of this step are not valid")
         self.cache.commit(dict(zip(plan.slots, plan.new_len)))
         return logits
 

@@ -240,6 +240,48 @@ def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilog
              _stream()), "skinny_gemm")
 
 
+USE_TC_GEMM = True      # False: many-token bfloat16 products go to the library (cuBLAS) instead
+
+
+def gemm_tc_ok(x: torch.Tensor, weight: torch.Tensor, gated: bool = False, sms: int = 148) -> bool:
+    """Whether the tcgen05 product kernel takes these operands and has enough
+    128 x 256 tiles of output to put one on every SM (fewer tiles would leave
+    SMs idle while the rest stream the weights)."""
+    out_cols = weight.shape[0] // 2 if gated else weight.shape[0]
+    tiles = ((x.shape[0] + 127) // 128) * ((out_cols + (127 if gated else 255)) // (128 if gated else 256))
+    return (USE_TC_GEMM and tiles >= sms and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and
+            x.shape[0] > SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and
+            weight.stride(1) == 1 and weight.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and
+            weight.data_ptr() % 16 == 0)
+
+
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "store",
+            activation: str = "gelu_tanh") -> None:
+    """out = x @ weight^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulation in tensor memory).
+
+    ``epilogue``: "store" (out bfloat16 or float32) or "gated" (weight = [Wg; Wu], out = act(x Wg^T) * (x Wu^T),
+    out width a multiple of 128)."""
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and out.stride(1) == 1
+    M, K = x.shape
+    N = out.shape[1]
+    code = {"store": 0, "gated": 1}[epilogue]
+    assert weight.shape == ((2 * N if code else N), K) and out.shape[0] == M
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"gemm_tc: unknown activation '{activation}'")
+    f = _fn("gemm_tc", "brolm_gemm_tc", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                         c_int, c_int, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K, code,
+             1 if out.dtype == torch.float32 else 0, ACTIVATIONS[activation], _stream()), "gemm_tc")
+
+
+def gemm_tc_status(reset: bool = False) -> int:
+    """0 if no bounded wait inside gemm_tc ever ran out; otherwise the code of the first one.  Synchronises."""
+    f = load_library("gemm_tc").brolm_gemm_tc_status
+    f.argtypes = [c_int]
+    f.restype = c_int
+    return f(1 if reset else 0)
+
+
 def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor, *, n_kv: int,
                    group: int, head_dim: int, scale: float, cap: float, window: int, batch: int, max_q_len: int,
                    k: Optional[torch.Tensor] = None, v: Optional[torch.Tensor] = None,
@@ -339,5 +381,5 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
 
 
 __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "embed_scale", "rmsnorm", "residual_rmsnorm",
-           "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_ok", "skinny_parts", "attention_simt", "attention_prefill_mma", "attention_decode_mma",
+           "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "attention_simt", "attention_prefill_mma", "attention_decode_mma",
            "decode_splits", "argmax", "sample"]

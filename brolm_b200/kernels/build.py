@@ -36,6 +36,7 @@ LIBRARIES: dict[str, list[str]] = {
     "attn_mma": ["attn_mma.cu"],
     "skinny_gemm": ["skinny_gemm.cu"],
     "attn_noalloc": ["attn_decode_noalloc.cu"],
+    "gemm_tc": ["gemm_tc.cu"],
     "sampling": ["sampling.cu"],
 }
 HEADERS = ["common.cuh", "attn_mma.cuh", "attn_decode_noalloc.h"]

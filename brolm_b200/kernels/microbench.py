@@ -127,7 +127,11 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=2304)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--no-tc", action="store_true", help="many-token products through the library instead of gemm_tc")
     args = ap.parse_args()
+    if args.no_tc:
+        from .. import kernels
+        kernels.USE_TC_GEMM = False
     {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "model_prefill": model_prefill,
      "norms": norms}[args.what](args)
 

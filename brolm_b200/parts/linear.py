@@ -5,8 +5,10 @@ element type in the same way).
 * float32 weight: the framework's own CUDA-core kernel, true 32-bit.
 * bfloat16 weight, up to 16 rows (decode steps): the framework's own
   weight-streaming tensor-core kernel, float32 accumulation.
-* bfloat16 weight, more rows: the library product (cuBLAS through torch),
-  float32 accumulation.  The result is bfloat16 or, on request, float32.
+* bfloat16 weight, more rows: the framework's tcgen05 kernel (TMA loads,
+  accumulator in tensor memory), float32 accumulation; the library product
+  (cuBLAS through torch) only for operands that kernel does not take (a width
+  that is no multiple of 8).  The result is bfloat16 or, on request, float32.
 """
 from __future__ import annotations
 
@@ -49,6 +51,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
             y = out if out is not None else torch.empty((M, N), dtype=want, device=x.device)
             kernels.skinny_gemm(x, weight, y)
             return y
+        if kernels.gemm_tc_ok(x, weight) and want in (torch.bfloat16, torch.float32):
+            y = out if out is not None else torch.empty((M, N), dtype=want, device=x.device)
+            if y.stride(1) == 1 and y.data_ptr() % 16 == 0:
+                kernels.gemm_tc(x, weight, y)
+                return y
         if want == torch.bfloat16:
             return torch.mm(x, weight.t(), out=out) if out is not None else torch.mm(x, weight.t())
         if out is not None:

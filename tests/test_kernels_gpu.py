@@ -176,6 +176,47 @@ def test_skinny_gemm_partial_sums_feed_the_residual_kernel(parts):
     assert kernels.skinny_parts(torch.empty(8, 2304), torch.empty(18432, 2304)) == 1
 
 
+@pytest.mark.parametrize("M,N,K", [(17, 256, 64), (128, 256, 256), (100, 300, 200), (333, 2304, 2048), (1000, 40, 72),
+                                   (2048, 512, 9216)])
+def test_gemm_tc(M, N, K):
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    ref = plain.linear(x, w)
+    for dt in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N), 7.0, dtype=dt, device=DEV)
+        kernels.gemm_tc(x.to(DEV), w.to(DEV), out)
+        close(out, ref, dt, scale=float(ref.abs().max()) * (50 if dt == torch.float32 else 1))
+    assert kernels.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("M,F,K,act", [(17, 128, 64, "gelu_tanh"), (300, 384, 200, "silu"), (2048, 9216, 2304, "gelu_tanh")])
+def test_gemm_tc_gated(M, F, K, act):
+    g = torch.Generator().manual_seed(F + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * F, K, generator=g) * 0.05).to(torch.bfloat16)
+    xd, wd = x.to(DEV), w.to(DEV)
+    out = torch.empty(M, F, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tc(xd, wd, out, "gated", act)
+    gate, up = xd.double() @ wd[:F].double().t(), xd.double() @ wd[F:].double().t()      # float64 on the device: fast
+    ref = (plain.gelu_tanh(gate) if act == "gelu_tanh" else gate * torch.sigmoid(gate)) * up
+    close(out, ref, torch.bfloat16)
+    assert kernels.gemm_tc_status() == 0
+
+
+def test_gemm_tc_strided_views():
+    g = torch.Generator().manual_seed(2)
+    big = torch.randn(40, 3 * 64, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(24, 64, generator=g).to(torch.bfloat16).to(DEV)
+    x = big[:, 64:128]
+    assert kernels.gemm_tc_ok(x, w, sms=1) and not kernels.gemm_tc_ok(big[:, 1:65], w, sms=1)
+    assert not kernels.gemm_tc_ok(x, w)            # one tile only: not worth a persistent kernel
+    wide = torch.zeros(40, 64, dtype=torch.float32, device=DEV)
+    kernels.gemm_tc(x, w, wide[:, 8:32])
+    close(wide[:, 8:32], plain.linear(x.cpu(), w.cpu()), torch.float32, scale=float(wide.abs().max()) * 50)
+    assert float(wide[:, :8].abs().max()) == 0 and float(wide[:, 32:].abs().max()) == 0
+
+
 def test_skinny_gemm_strided_input():
     g = torch.Generator().manual_seed(1)
     big = torch.randn(5, 3 * 64, generator=g).to(torch.bfloat16).to(DEV)
