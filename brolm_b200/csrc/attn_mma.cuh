@@ -330,6 +330,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
 
     const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    pdl_wait();               // q and the newest key and value come from the kernels before this one
     const int kv_len = a.kv_len[b];
     const int n_q = a.n_kv * a.group;
     const int window = a.window > 0 ? a.window : 0x3fffffff;
@@ -463,6 +464,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
         }
     }
     cp_async_wait<0>();
+    pdl_trigger();                             // the keys are read: the next kernel may move in
     __syncthreads();                           // the stages are free: they now hold the warps' partial results
 
     // merge the four warps.  Layout in shared memory (float):
@@ -531,6 +533,8 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restri
     extern __shared__ float factor[];                 // [n_splits], then scratch for the block reductions
     float* scratch = factor + n_splits;
     const int head = blockIdx.x, b = blockIdx.y;
+    pdl_trigger();
+    pdl_wait();
     const size_t slot0 = ((size_t)b * n_q + head) * n_splits;
     float mx = -INFINITY;
     for (int s = threadIdx.x; s < n_splits; s += blockDim.x) mx = fmaxf(mx, part_ml[(slot0 + s) * 2]);
@@ -577,13 +581,12 @@ int launch_decode(const MmaArgs& a, int batch, cudaStream_t stream) {
         allowed = smem;
     }
     dim3 grid(a.n_splits, a.n_kv, batch);
-    attn_decode_mma_kernel<HD_MAX, EXACT><<<grid, NTHREADS, smem, stream>>>(a);
-    int st = launch_status();
+    int st = launch_pdl(attn_decode_mma_kernel<HD_MAX, EXACT>, grid, dim3(NTHREADS), smem, stream, a);
     if (st != 0 || a.n_splits == 1) return st;
     dim3 cgrid(a.n_kv * a.group, batch);
-    attn_combine_kernel<<<cgrid, 128, (a.n_splits + 33) * sizeof(float), stream>>>(a.part_o, a.part_ml, a.out, a.cu_q, a.out_stride, a.n_kv * a.group,
-                                                   a.n_splits, a.hd);
-    return launch_status();
+    return launch_pdl(attn_combine_kernel, cgrid, dim3(128), (a.n_splits + 33) * sizeof(float), stream,
+                      (const float*)a.part_o, (const float*)a.part_ml, a.out, a.cu_q, a.out_stride,
+                      a.n_kv * a.group, a.n_splits, a.hd);
 }
 
 int check_common(int hd, int group, int n_kv, int q_stride, int out_stride, int batch) {

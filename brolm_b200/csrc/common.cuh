@@ -7,6 +7,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define BROLM_API extern "C" __attribute__((visibility("default")))
 
@@ -105,4 +106,38 @@ __device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
 
 static inline int launch_status() {
     return (int)cudaGetLastError();
+}
+
+// Programmatic dependent launch.  A kernel launched through launch_pdl may begin
+// while the kernel before it in the stream is still running; it must call
+// pdl_wait() before it touches anything that kernel (or any earlier one) wrote,
+// and may do work that depends on nothing before it (index arithmetic, fetching
+// weights).  pdl_trigger() lets the kernel after this one start launching.
+// The environment variable BROLM_NO_PDL=1 falls back to plain stream order.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("BROLM_NO_PDL");
+        on = (e && e[0] == '1') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }

@@ -72,6 +72,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const X* __restrict__ x, c
                                                       O* __restrict__ out, int hidden) {
     __shared__ float scratch[33];
     const int r = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
     const X* src = x + (size_t)(rows ? rows[r] : r) * hidden;
     O* dst = out + (size_t)r * hidden;
     if (MAXC == 0) {
@@ -124,11 +126,13 @@ template <typename X, typename W, typename O>
 static int rmsnorm_launch(const void* x, const void* rows, const void* w, float eps, float offset, void* out, int n,
                           int hidden, cudaStream_t s) {
     const int c = vec_chunks(hidden, x, w, out, nullptr);
-#define BROLM_RMS(C) rmsnorm_kernel<X, W, O, C><<<n, 256, 0, s>>>((const X*)x, (const int32_t*)rows, (const W*)w, eps, \
-                                                                  offset, (O*)out, hidden)
-    if (c == 1) BROLM_RMS(1); else if (c == 4) BROLM_RMS(4); else if (c == 8) BROLM_RMS(8); else BROLM_RMS(0);
+#define BROLM_RMS(C) launch_pdl(rmsnorm_kernel<X, W, O, C>, dim3(n), dim3(256), 0, s, (const X*)x, (const int32_t*)rows, \
+                                (const W*)w, eps, offset, (O*)out, hidden)
+    if (c == 1) return BROLM_RMS(1);
+    if (c == 4) return BROLM_RMS(4);
+    if (c == 8) return BROLM_RMS(8);
+    return BROLM_RMS(0);
 #undef BROLM_RMS
-    return launch_status();
 }
 
 template <typename X, typename W>
@@ -173,7 +177,9 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
     float* hr = h + (size_t)r * hidden;
     const Y* yr = y + (size_t)r * hidden;
     O* dst = out + (size_t)r * hidden;
+    pdl_trigger();
     if (MAXC == 0) {
+        pdl_wait();
         auto y_at = [&](int i) {
             float v = to_float(yr[i]);
             for (int s = 1; s < n_parts; ++s) v += to_float(yr[(size_t)s * part_stride + i]);
@@ -207,11 +213,23 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
     }
     constexpr int C = MAXC > 0 ? MAXC : 1;
     float v[C][4], res[C][4], gp[C][4], gn[C][4];
+    // the gains are weights: fetched while the kernel before this one finishes
 #pragma unroll
     for (int c = 0; c < C; ++c) {
         const int i = (c * 256 + threadIdx.x) * 4;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) v[c][e] = res[c][e] = gp[c][e] = gn[c][e] = 0.0f;
+        for (int e = 0; e < 4; ++e) gp[c][e] = gn[c][e] = 0.0f;
+        if (i < hidden) {
+            if (w_post) load4(w_post + i, gp[c]);
+            if (w_next) load4(w_next + i, gn[c]);
+        }
+    }
+    pdl_wait();
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int i = (c * 256 + threadIdx.x) * 4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[c][e] = res[c][e] = 0.0f;
         if (i < hidden) {
             load4(yr + i, v[c]);
             for (int s = 1; s < n_parts; ++s) {
@@ -221,8 +239,6 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
                 for (int e = 0; e < 4; ++e) v[c][e] += t[e];
             }
             load4(hr + i, res[c]);
-            if (w_post) load4(w_post + i, gp[c]);
-            if (w_next) load4(w_next + i, gn[c]);
         }
     }
     if (w_post) {
@@ -268,11 +284,13 @@ static int residual_launch(void* h, const void* y, int n_parts, long long part_s
                            cudaStream_t s) {
     int c = vec_chunks(hidden, h, y, w_post, w_next);
     if (c && (((uintptr_t)out & 15) || part_stride % 4 != 0)) c = 0;
-#define BROLM_RES(C) residual_rmsnorm_kernel<Y, W, O, C><<<n, 256, 0, s>>>((float*)h, (const Y*)y, n_parts, part_stride, (const W*)w_post, \
-        eps_post, off_post, (const W*)w_next, eps_next, off_next, (O*)out, hidden)
-    if (c == 1) BROLM_RES(1); else if (c == 4) BROLM_RES(4); else if (c == 8) BROLM_RES(8); else BROLM_RES(0);
+#define BROLM_RES(C) launch_pdl(residual_rmsnorm_kernel<Y, W, O, C>, dim3(n), dim3(256), 0, s, (float*)h, (const Y*)y, \
+        n_parts, part_stride, (const W*)w_post, eps_post, off_post, (const W*)w_next, eps_next, off_next, (O*)out, hidden)
+    if (c == 1) return BROLM_RES(1);
+    if (c == 4) return BROLM_RES(4);
+    if (c == 8) return BROLM_RES(8);
+    return BROLM_RES(0);
 #undef BROLM_RES
-    return launch_status();
 }
 
 template <typename Y, typename W>
@@ -374,6 +392,8 @@ __global__ void __launch_bounds__(256) rope_kv_write_vec_kernel(bf16* __restrict
                                                                 const int32_t* __restrict__ cache_rows,
                                                                 int page_size) {
     const int t = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
     const int pos = positions[t];
     if (pos < 0) return;
     const int half = hd >> 1, per_head = half >> 3;
@@ -423,10 +443,9 @@ BROLM_API int brolm_rope_kv_write(void* qkv, int dtype, const void* positions, c
         int items = (n_q + 2 * n_kv) * (hd >> 4);
         int th = (items + 31) / 32 * 32;
         if (th > 256) th = 256;
-        rope_kv_write_vec_kernel<<<tokens, th, 0, stream>>>((bf16*)qkv, (const int32_t*)positions,
-                                                            (const float2*)cos_sin, n_q, n_kv, hd, (bf16*)k_pages,
-                                                            (bf16*)v_pages, (const int32_t*)cache_rows, page_size);
-        return launch_status();
+        return launch_pdl(rope_kv_write_vec_kernel, dim3(tokens), dim3(th), 0, stream, (bf16*)qkv,
+                          (const int32_t*)positions, (const float2*)cos_sin, n_q, n_kv, hd, (bf16*)k_pages,
+                          (bf16*)v_pages, (const int32_t*)cache_rows, page_size);
     }
     dim3 grid(tokens, n_q + 2 * n_kv);
     int threads = ((hd >> 1) + 31) / 32 * 32;

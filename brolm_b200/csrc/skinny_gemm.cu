@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
     const int kb_first = blockIdx.y * per, nkb = min(nkb_all, kb_first + per);
     uint4 wc[2][MT][2], xc[2][NT];                                 // [half of the block][tile][row r / r + 8]
 
-    auto load = [&](int kb, uint4 (&wv)[2][MT][2], uint4 (&xv)[2][NT]) {
+    auto load_w = [&](int kb, uint4 (&wv)[2][MT][2]) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int kk = kb * KB + h * 32 + q * 8;
@@ -105,21 +105,31 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
                 wv[h][i][0] = ldg16(a.w + (size_t)(wrow[i] + r) * a.ldw + kk, kok && col < n_limit);
                 wv[h][i][1] = ldg16(a.w + (size_t)(wrow[i] + r + 8) * a.ldw + kk, kok && col + 8 < n_limit);
             }
+        }
+    };
+    auto load_x = [&](int kb, uint4 (&xv)[2][NT]) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int kk = kb * KB + h * 32 + q * 8;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const int tok = j * 8 + r;
-                xv[h][j] = ldg16_cached(a.x + (size_t)tok * a.ldx + kk, kok && tok < a.M);
+                xv[h][j] = ldg16_cached(a.x + (size_t)tok * a.ldx + kk, kk < a.K && tok < a.M);
             }
         }
     };
     (void)w_rows;
 
+    // The weights depend on nothing that ran before: their first loads go out while the kernel
+    // before this one is still finishing; X is its output and has to wait.
     int kb = kb_first + warp;
-    if (kb < nkb) load(kb, wc, xc);
+    if (kb < nkb) load_w(kb, wc);
+    pdl_wait();
+    if (kb < nkb) load_x(kb, xc);
     for (; kb < nkb; kb += WARPS) {
         uint4 wn[2][MT][2], xn[2][NT];
         const bool more = kb + WARPS < nkb;
-        if (more) load(kb + WARPS, wn, xn);
+        if (more) { load_w(kb + WARPS, wn); load_x(kb + WARPS, xn); }
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
@@ -141,6 +151,10 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
             }
         }
     }
+
+    // The stream of weights is over: the next kernel may take its place on the SMs now.  (Letting it in
+    // earlier packs its blocks onto the few SMs that happen to have room, and they then run unevenly.)
+    pdl_trigger();
 
     // partial sums of the warps -> shared memory, then summed in warp order
 #pragma unroll
@@ -183,8 +197,7 @@ template <int MT, int NT, int EPI>
 int launch(const SkinnyArgs& a, cudaStream_t stream) {
     constexpr int cols = (EPI == EPI_GATED ? MT / 2 : MT) * 16;
     dim3 blocks((a.N + cols - 1) / cols, a.ksplit);
-    skinny_kernel<MT, NT, EPI><<<blocks, WARPS * 32, 0, stream>>>(a);
-    return launch_status();
+    return launch_pdl(skinny_kernel<MT, NT, EPI>, blocks, dim3(WARPS * 32), 0, stream, a);
 }
 
 template <int EPI>
