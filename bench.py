@@ -147,7 +147,12 @@ def main() -> int:
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # larger than the 126 MB L2
 
     def decode_run(batch: int, context: int, steps: int, warmup: int):
-        """(tokens/s on the device, ms per step, e2e tokens/s, launches, clocks, bytes in, bytes out)."""
+        """Decode ``steps`` tokens per sequence after ``warmup`` untimed ones, ending at ``context`` tokens.
+
+        Two passes over the same prompts.  End to end: ``brolm_b200.generate`` with host token ids in and
+        out; every step copies the step's tokens from pinned host memory to the device and reads the
+        sampled ids back.  Device: the same steps fed with the tokens the first pass produced, queued
+        without reading anything back, timed with CUDA events."""
         total = steps + warmup
         prompt_len = context - total - 1
         engine = bb.Engine(model, max_tokens=batch * ((context + 63) // 64 * 64), max_slots=batch,
@@ -157,26 +162,43 @@ def main() -> int:
         opts = bb.GenerateOptions(max_new_tokens=total + 1, sampling=bb.SamplingParams(temperature=0.0),
                                   stop_on_eos=False)
         stamps: list[float] = []
-        events: list = []
-        launches: list[int] = []
 
         def on_step(produced: int, active: int) -> None:
             # called after the step's tokens reached the host
             stamps.append(time.perf_counter())
-            ev = torch.cuda.Event(enable_timing=True)
             flush.zero_()                                   # between steps: push the weights out of L2
-            ev.record()
-            events.append(ev)
-            launches.append(kernels.launch_count())
 
         with ClockSampler() as clocks:
             out = bb.generate(engine, prompts, eos_id=-1, opts=opts, on_step=on_step)
             torch.cuda.synchronize()
-        assert all(len(o) == total + 1 for o in out)
-        # on_step 0 follows the prefill; steps 1..warmup are warm-up; the rest are timed
-        a, b = warmup, warmup + steps
-        dev_ms = events[a].elapsed_time(events[b])
-        # the flush between steps is inside the device window: time it alone and take it out
+            assert all(len(o) == total + 1 for o in out)
+            # on_step 0 follows the prefill; steps 1..warmup are warm-up; the rest are timed
+            e2e_s = stamps[warmup + steps] - stamps[warmup]
+
+            # device pass: the same tokens, nothing read back
+            sampler = bb.Sampler(opts.sampling)
+            streams = torch.arange(batch, dtype=torch.int32, device=dev)
+            slots = engine.open(batch)
+            engine.step(slots, prompts)
+            events = []
+            launches = []
+            for i in range(total):
+                if i >= warmup:
+                    ev = torch.cuda.Event(enable_timing=True)
+                    ev.record()
+                    events.append(ev)
+                    launches.append(kernels.launch_count())
+                flush.zero_()
+                logits = engine.step(slots, [[o[i]] for o in out])
+                sampler(logits, streams, i + 1)
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            events.append(ev)
+            launches.append(kernels.launch_count())
+            torch.cuda.synchronize()
+            engine.close(slots)
+        dev_ms = events[0].elapsed_time(events[-1])
+        # the flush between steps is inside both windows: time it alone and take it out
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record()
         for _ in range(steps):
@@ -184,11 +206,10 @@ def main() -> int:
         f1.record()
         torch.cuda.synchronize()
         flush_ms = f0.elapsed_time(f1)
-        e2e_s = stamps[b] - stamps[a]
         ms = (dev_ms - flush_ms) / steps
         return {"tok_s": batch * 1000.0 / ms, "ms": ms, "e2e_tok_s": batch * steps / (e2e_s - flush_ms / 1000.0),
-                "launches": launches[b] - launches[a], "clocks": clocks.summary(),
-                "h2d": 4 * batch, "d2h": 4 * batch}
+                "launches": launches[-1] - launches[0], "clocks": clocks.summary(),
+                "h2d": engine.last_h2d_bytes, "d2h": 4 * batch}
 
     main_run = decode_run(args.batch, args.context, args.steps, args.warmup)
     bytes_step = decode_bytes(cfg, layers, args.batch, args.context)
@@ -219,6 +240,10 @@ def main() -> int:
         for b in (1, 64):
             r = decode_run(b, args.context, max(8, args.steps // 4), 3)
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
+        # the workload of the configuration's own description: prompts of 1,024 tokens, 256 generated
+        for b in (1, 8, 64):
+            r = decode_run(b, 1024 + 256, max(8, args.steps // 2), 3)
+            points[f"decode_b{b}_ctx1280"] = round(r["tok_s"], 1)
         result["points"] = points
         # prefill of 2,048 tokens, one sequence, logits of the last token
         T = 2048

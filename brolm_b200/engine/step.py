@@ -54,6 +54,7 @@ class _DecodeGraph:
 
     def __init__(self, engine: "Engine", rows: int, kv_cap: int):
         cache, dev = engine.cache, engine.device
+        self.engine = engine
         self.rows, self.kv_cap = rows, kv_cap
         self.widths = []
         for g in cache.kv_groups:
@@ -94,8 +95,10 @@ class _DecodeGraph:
         self.copied = torch.cuda.Event()
         self.copied.record()
         self.graph = torch.cuda.CUDAGraph()
+        before = kernels.launch_count()
         with torch.cuda.graph(self.graph, pool=engine._graph_pool):
             self.logits = engine.model.forward(self.ctx, self.tokens, self.all_rows)
+        self.kernels = kernels.launch_count() - before      # this library's kernels in one replay
 
     def run(self, plan: _Plan, cache: Cache) -> torch.Tensor:
         R, B = self.rows, len(plan.slots)
@@ -117,7 +120,9 @@ class _DecodeGraph:
             hv[off + g * R:off + g * R + B] = cache.write_rows(g, plan.slots, plan.old, plan.new_len)
         self.dev.copy_(self.host, non_blocking=True)
         self.copied.record()
+        self.engine.last_h2d_bytes = self.host.numel() * 4
         self.graph.replay()
+        kernels.add_launches(self.kernels)
         return self.logits
 
 
@@ -134,6 +139,7 @@ class Engine:
         self.use_graphs = bool(use_graphs and self.device.type == "cuda" and all(p.graph_safe for p in parts))
         self._graphs: dict[tuple, _DecodeGraph] = {}
         self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
+        self.last_h2d_bytes = 0          # bytes the last step copied from the host
 
     # slots ----------------------------------------------------------------
     def open(self, n: int = 1) -> list[int]:
@@ -241,6 +247,7 @@ class Engine:
         for p, o in zip(parts, offs[:-1]):
             hv[o:o + p.size] = p
         dev = host.to(self.device, non_blocking=True)
+        self.last_h2d_bytes = host.numel() * 4
         seg = [dev[int(o):int(o) + s] for o, s in zip(offs[:-1], sizes)]
         page_tables = [seg[7 + g].view(B, tables[g].shape[1]) for g in range(len(tables))]
         cache_rows = [seg[7 + len(tables) + g] for g in range(len(tables))]

@@ -56,6 +56,12 @@ def launch_count() -> int:
     return _launches
 
 
+def add_launches(n: int) -> None:
+    """Count kernels that ran without passing through this module (a replayed CUDA graph)."""
+    global _launches
+    _launches += n
+
+
 def _check(status: int, what: str) -> None:
     global _launches
     if status == 0:
