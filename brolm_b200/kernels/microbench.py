@@ -14,7 +14,8 @@ import math
 
 import torch
 
-from . import attention_decode_mma, attention_prefill_mma, decode_splits, residual_rmsnorm, rmsnorm
+from . import (attention_decode_mma, attention_prefill_mma, decode_splits, gemm_tc, gemm_tc_status, residual_rmsnorm,
+               rmsnorm, skinny_gemm)
 
 DEV = "cuda:0"
 
@@ -100,6 +101,39 @@ def model_prefill(args) -> None:
     print(f"model_prefill layers={args.layers} tokens={args.tokens}: {ms:.3f} ms")
 
 
+def skinny(args) -> None:
+    """The few-token products of one Gemma 2 2B layer at --batch tokens (weights streamed once each)."""
+    B, H, F = args.batch, args.hidden, args.inter
+    qkv = (args.heads + 2 * args.kv_heads) * args.head_dim
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    for name, n, k, epi in (("qkv", qkv, H, "store"), ("o", H, args.heads * args.head_dim, "store"),
+                            ("gate_up+act", F, H, "gated"), ("down", H, F, "store")):
+        x = torch.randn(B, k, device=DEV).to(torch.bfloat16)
+        w = torch.randn(2 * n if epi == "gated" else n, k, device=DEV).to(torch.bfloat16)
+        out = torch.empty(B, n, dtype=torch.bfloat16, device=DEV)
+        ms = timed(lambda: skinny_gemm(x, w, out, epi), args.reps, flush)
+        print(f"skinny {name} rows={B} N={w.shape[0]} K={k}: {ms * 1e3:.1f} us, {w.numel() * 2 / ms / 1e6:.0f} GB/s of weights")
+
+
+def gemm(args) -> None:
+    """The many-token products of one Gemma 2 2B layer at --tokens tokens on tcgen05, against the library."""
+    T, H, F = args.tokens, args.hidden, args.inter
+    qkv = (args.heads + 2 * args.kv_heads) * args.head_dim
+    for name, n, k, epi in (("qkv", qkv, H, "store"), ("o", H, args.heads * args.head_dim, "store"),
+                            ("gate_up+act", F, H, "gated"), ("down", H, F, "store")):
+        x = torch.randn(T, k, device=DEV).to(torch.bfloat16)
+        rows = 2 * n if epi == "gated" else n
+        w = torch.randn(rows, k, device=DEV).to(torch.bfloat16)
+        out = torch.empty(T, n, dtype=torch.bfloat16, device=DEV)
+        wide = torch.empty(T, rows, dtype=torch.bfloat16, device=DEV)
+        ms = timed(lambda: gemm_tc(x, w, out, epi), args.reps)
+        lib = timed(lambda: torch.mm(x, w.t(), out=wide), args.reps)
+        fl = 2.0 * T * rows * k
+        print(f"gemm_tc {name} M={T} N={rows} K={k}: {ms * 1e3:.1f} us, {fl / ms / 1e9:.0f} TFLOP/s "
+              f"(library product alone, without the activation: {lib * 1e3:.1f} us, {fl / lib / 1e9:.0f} TFLOP/s)")
+    print("gemm_tc status", gemm_tc_status())
+
+
 def norms(args) -> None:
     B, H = args.batch, args.hidden
     h = torch.randn(B, H, device=DEV)
@@ -115,7 +149,8 @@ def norms(args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "model_prefill", "norms"])
+    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "model_prefill", "norms", "skinny", "gemm"])
+    ap.add_argument("--inter", type=int, default=9216)
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=8192)
@@ -133,7 +168,7 @@ def main() -> None:
         from .. import kernels
         kernels.USE_TC_GEMM = False
     {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "model_prefill": model_prefill,
-     "norms": norms}[args.what](args)
+     "norms": norms, "skinny": skinny, "gemm": gemm}[args.what](args)
 
 
 if __name__ == "__main__":
