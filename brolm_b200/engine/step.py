@@ -172,9 +172,10 @@ class Engine:
             ctx, tok_dev, rows = self._context(plan)
             logits = self.model.forward(ctx, tok_dev, rows)
             if plan.mode == "prefill" and self.model.dtype == torch.bfloat16 and self.device.type == "cuda":
-                code = kernels.gemm_tc_status(reset=True)      # waits for the step; 0 unless a bounded wait ran out
+                # waits for the step; 0 unless a bounded wait inside a tcgen05 kernel ran out
+                code = kernels.gemm_tc_status(reset=True) or kernels.attention_tc_status(reset=True)
                 if code:
-                    raise StepError(f"step: a wait inside the tensor-core product kernel ran out (code {code}); "
+                    raise StepError(f"step: a wait inside a tensor-core kernel ran out (code {code}); "
                                     f"the results of this step are not valid")
         self.cache.commit(dict(zip(plan.slots, plan.new_len)))
         return logits

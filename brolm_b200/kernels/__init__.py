@@ -328,6 +328,34 @@ def attention_prefill_mma(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor
              head_dim, scale, cap, window, batch, max_q_len, _stream()), "attention_prefill_mma")
 
 
+def attention_prefill_tc_ok(head_dim: int, group: int) -> bool:
+    """Whether the tcgen05 prompt-attention kernel takes these sizes."""
+    return head_dim in (64, 128, 256) and group > 0 and 128 % group == 0
+
+
+def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
+                         n_kv: int, group: int, head_dim: int, scale: float, cap: float, window: int, batch: int,
+                         max_q_len: int, v_lbo: int = 0, v_sbo: int = 0) -> None:
+    """tcgen05 attention of whole prompts that start at position 0 (bfloat16; head_dim 64, 128 or 256)."""
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
+    assert q.stride(-1) == 1 and out.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
+    assert k.stride(0) == v.stride(0) and cu_q.dtype == torch.int32 and q.shape[0] == k.shape[0] == v.shape[0]
+    f = _fn("attn_tc", "brolm_attn_prefill_tc", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                 c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int,
+                                                 c_int, c_int, c_void_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cu_q), _ptr(k), _ptr(v), k.stride(0), q.shape[0],
+             n_kv, group, head_dim, scale, cap, window, batch, max_q_len, v_lbo, v_sbo, _stream()),
+           "attention_prefill_tc")
+
+
+def attention_tc_status(reset: bool = False) -> int:
+    """0 if no bounded wait inside the tcgen05 attention ever ran out; otherwise its code.  Synchronises."""
+    f = load_library("attn_tc").brolm_attn_tc_status
+    f.argtypes = [c_int]
+    f.restype = c_int
+    return f(1 if reset else 0)
+
+
 def decode_splits(batch: int, n_kv: int, max_kv_len: int, window: int, sms: int = 148) -> int:
     """How many blocks share the keys of one (sequence, kv head): about two
     waves of blocks over the SMs, at least two pages per block."""
@@ -387,5 +415,5 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
 
 
 __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "embed_scale", "rmsnorm", "residual_rmsnorm",
-           "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "attention_simt", "attention_prefill_mma", "attention_decode_mma",
+           "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_tc_status", "attention_decode_mma",
            "decode_splits", "argmax", "sample"]

@@ -37,6 +37,7 @@ LIBRARIES: dict[str, list[str]] = {
     "skinny_gemm": ["skinny_gemm.cu"],
     "attn_noalloc": ["attn_decode_noalloc.cu"],
     "gemm_tc": ["gemm_tc.cu"],
+    "attn_tc": ["attn_tc.cu"],
     "sampling": ["sampling.cu"],
 }
 HEADERS = ["common.cuh", "attn_mma.cuh", "attn_decode_noalloc.h"]

@@ -14,7 +14,7 @@ import math
 
 import torch
 
-from . import (attention_decode_mma, attention_prefill_mma, decode_splits, gemm_tc, gemm_tc_status, residual_rmsnorm,
+from . import (attention_decode_mma, attention_prefill_mma, attention_prefill_tc, attention_tc_status, decode_splits, gemm_tc, gemm_tc_status, residual_rmsnorm,
                rmsnorm, skinny_gemm)
 
 DEV = "cuda:0"
@@ -77,11 +77,18 @@ def attn_prefill(args) -> None:
                               qkv[:, (n_q + n_kv) * hd:], n_kv=n_kv, group=n_q // n_kv, head_dim=hd,
                               scale=1 / math.sqrt(hd), cap=50.0, window=args.window, batch=1, max_q_len=T)
 
-    ms = timed(run, args.reps)
+    def run_tc():
+        attention_prefill_tc(qkv[:, :n_q * hd], out, cu, qkv[:, n_q * hd:(n_q + n_kv) * hd],
+                             qkv[:, (n_q + n_kv) * hd:], n_kv=n_kv, group=n_q // n_kv, head_dim=hd,
+                             scale=1 / math.sqrt(hd), cap=50.0, window=args.window, batch=1, max_q_len=T)
+
     w = args.window or T
     keys = sum(min(p + 1, w) for p in range(T))
     flops = 4.0 * n_q * hd * keys
-    print(f"attn_prefill tokens={T} window={args.window}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.1f} TFLOP/s")
+    for name, fn in (("tcgen05", run_tc), ("mma.sync", run)):
+        ms = timed(fn, args.reps)
+        print(f"attn_prefill {name} tokens={T} window={args.window}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.1f} TFLOP/s")
+    print("attention_tc status", attention_tc_status())
 
 
 def model_prefill(args) -> None:

@@ -91,7 +91,9 @@ class Attention(Part):
         return ctx.dtype == torch.bfloat16 and self.head_dim <= 256 and self.n_q // self.n_kv <= 16
 
     def attend_packed(self, q, k, v, out, ctx, common):
-        if self._tensor_cores(ctx):
+        if self._tensor_cores(ctx) and kernels.attention_prefill_tc_ok(self.head_dim, self.n_q // self.n_kv):
+            kernels.attention_prefill_tc(q, out, ctx.cu_q, k, v, **common)         # tcgen05, scores in tensor memory
+        elif self._tensor_cores(ctx):
             kernels.attention_prefill_mma(q, out, ctx.cu_q, k, v, **common)
         else:
             kernels.attention_simt(q, out, ctx.cu_q, ctx.kv_len, k=k, v=v, **common)

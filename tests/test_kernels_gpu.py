@@ -305,11 +305,15 @@ def _attention_oracle(q, k, v, n_q, n_kv, hd, scale, cap, window):
     return plain.attention(q, k, v, n_q, n_kv, hd, scale, cap, window)
 
 
-@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "simt"), (torch.bfloat16, "simt"), (torch.bfloat16, "mma")])
+@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "simt"), (torch.bfloat16, "simt"), (torch.bfloat16, "mma"),
+                                          (torch.bfloat16, "tc")])
 @pytest.mark.parametrize("n_q,n_kv,hd,window,cap", [(4, 2, 16, 8, 50.0), (6, 1, 32, 16, 20.0), (3, 3, 48, 0, 0.0),
                                                     (8, 4, 256, 100, 50.0), (5, 5, 128, 0, 30.0), (8, 1, 64, 33, 0.0),
-                                                    (16, 1, 80, 70, 10.0)])
+                                                    (16, 1, 80, 70, 10.0), (4, 2, 64, 0, 50.0), (32, 16, 128, 0, 50.0),
+                                                    (8, 8, 256, 0, 0.0)])
 def test_attention_packed(dtype, kernel, n_q, n_kv, hd, window, cap):
+    if kernel == "tc" and not kernels.attention_prefill_tc_ok(hd, n_q // n_kv):
+        pytest.skip("sizes the tcgen05 kernel leaves to the mma.sync kernel")
     g = torch.Generator().manual_seed(hd + n_q)
     lengths = [1, 37, 150, 64, 300]
     T = sum(lengths)
@@ -324,6 +328,9 @@ def test_attention_packed(dtype, kernel, n_q, n_kv, hd, window, cap):
     kk, vv = dq[:, n_q * hd:(n_q + n_kv) * hd], dq[:, (n_q + n_kv) * hd:]
     if kernel == "mma":
         kernels.attention_prefill_mma(dq[:, :n_q * hd], out, cu, kk, vv, **kw)
+    elif kernel == "tc":
+        kernels.attention_prefill_tc(dq[:, :n_q * hd], out, cu, kk, vv, **kw)
+        assert kernels.attention_tc_status() == 0
     else:
         kernels.attention_simt(dq[:, :n_q * hd], out, cu, torch.tensor(lengths, dtype=torch.int32, device=DEV),
                                k=kk, v=vv, **kw)
