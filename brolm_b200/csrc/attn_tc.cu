@@ -13,11 +13,12 @@
 //             size) into the output accumulator in tensor memory; the values
 //             are used as they lie in memory (keys x head size, an MN-major
 //             operand), so nothing is transposed;
-//   warps 2-5 softmax: thread r owns row r.  It reads its 64 scores with
-//             tcgen05.ld, applies scale, soft-cap and mask, keeps the running
-//             reference maximum and sum, writes the probabilities as bfloat16
-//             into shared memory (the A operand of the second product), and at
-//             the end scales the accumulator by 1 / sum and stores it.
+//   warps 2-9 softmax: two threads own each row, 32 of the tile's 64 scores
+//             each.  A thread reads its scores with tcgen05.ld, applies scale,
+//             soft-cap and mask, agrees with its partner on the row's reference
+//             maximum, writes the probabilities as bfloat16 into shared memory
+//             (the A operand of the second product, two buffers), and at the
+//             end scales its half of the accumulator by 1 / sum and stores it.
 //
 // The reference maximum of a row is only raised when the tile's maximum exceeds
 // it by more than 8 (in log2 units): probabilities then stay below 2^8, and the
@@ -37,7 +38,7 @@
 namespace {
 
 constexpr int BM = 128, BN = 64;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;      // loader warp, issuer warp, eight softmax warps
 constexpr int TMEM_COLS = 512;
 constexpr long long WAIT_CYCLES = 2000000000ll;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -138,29 +139,28 @@ __device__ __forceinline__ float fast_rcp(float x) {
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ float score_of(float s, float scale, float cap, float inv_cap) {
-    s *= scale;
-    if (cap > 0.0f) s = cap * (1.0f - 2.0f * fast_rcp(1.0f + fast_exp2(s * inv_cap * (2.0f * LOG2E))));
-    return s * LOG2E;
-}
-
 // barrier slots
 enum : int { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13,
-             PV_DONE = 14, N_BARS = 15 };
+             PV_DONE = 15, N_BARS = 17 };
 
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                      const __grid_constant__ CUtensorMap map_k,
                                                                      const __grid_constant__ CUtensorMap map_v, TcArgs a) {
     constexpr int DB = HD / 64;                          // 64-wide blocks of the head size
-    constexpr int Q_BYTES = BM * HD * 2, KV_BYTES = BN * HD * 2, P_BYTES = BM * BN * 2;
+    constexpr int Q_BYTES = BM * HD * 2, KV_BYTES = BN * HD * 2, P_BYTES = BM * BN * 2;      // P: two buffers
     constexpr uint32_t S_COL = 0, O_COL = 2 * BN;        // tensor-memory columns: two score buffers, then the output
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) uint8_t smem_raw[];     // the swizzled tiles need 1024-byte alignment
+    uint8_t* base = smem_raw;
+    if ((smem_u32(base) & 1023u) != 0) {                      // never seen; refuse rather than compute wrongly
+        if (threadIdx.x == 0) atomicCAS(&g_attn_tc_error, 0, 13);
+        return;
+    }
     const uint32_t q_s = smem_u32(base), k_s = q_s + Q_BYTES, v_s = k_s + 2 * KV_BYTES, p_s = v_s + 2 * KV_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base + Q_BYTES + 4 * KV_BYTES + P_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + Q_BYTES + 4 * KV_BYTES + 2 * P_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
     volatile int* give_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars + N_BARS) + 16);   // [2][2][BM]: maxima by tile parity and half; the sums reuse it
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * i; };
 
@@ -189,10 +189,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
             mbar_init(bar(V_FULL + s), 1);
             mbar_init(bar(V_EMPTY + s), 1);
             mbar_init(bar(S_FULL + s), 1);
-            mbar_init(bar(S_EMPTY + s), 4);
+            mbar_init(bar(S_EMPTY + s), 8);
+            mbar_init(bar(P_FULL + s), 8);
+            mbar_init(bar(PV_DONE + s), 1);
         }
-        mbar_init(bar(P_FULL), 4);
-        mbar_init(bar(PV_DONE), 1);
         give_up[0] = 0;
         give_up[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -262,10 +262,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles) { ok = issue_qk(j + 1); if (!ok) break; }
                 const int s = j & 1;
-                ok = mbar_wait(bar(P_FULL), j & 1, give_up, 6) && mbar_wait(bar(V_FULL + s), (j >> 1) & 1, give_up, 7);
+                ok = mbar_wait(bar(P_FULL + s), (j >> 1) & 1, give_up, 6) && mbar_wait(bar(V_FULL + s), (j >> 1) & 1, give_up, 7);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t pa = desc_kmajor(p_s);
+                const uint64_t pa = desc_kmajor(p_s + s * P_BYTES);
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k) {
                     // sixteen keys further: 32 bytes along a row of P, sixteen 128-byte rows down in V
@@ -273,26 +273,29 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
                     umma(tmem + O_COL, pa + 2 * k, vb, id_pv, (j | k) != 0);
                 }
                 umma_commit(bar(V_EMPTY + s));
-                umma_commit(bar(PV_DONE));
+                umma_commit(bar(PV_DONE + s));
             }
         }
     } else if (n_tiles > 0) {
-        const int quarter = warp & 3;
+        // Two warps share each quarter of the rows (a warp may only read the 32 lanes of tensor memory of its
+        // quarter): warp w and warp w + 4 own the same 32 rows, the first takes score columns 0-31, the second
+        // 32-63.  They agree on the row's reference maximum through shared memory and a 64-thread barrier.
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;                  // this thread's row of the block
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const bool row_ok = r < rows_here;
         const int pos = tok0 + r / a.group;                 // position of the row's token (prompts start at 0)
-        const float inv_cap = a.cap > 0.0f ? 1.0f / a.cap : 0.0f;
-        float m_ref = -INFINITY, l = 0.0f;
+        const float c0 = a.cap > 0.0f ? a.scale / a.cap * (2.0f * LOG2E) : a.scale * LOG2E;
+        const float c1 = a.cap * LOG2E, c2 = 2.0f * a.cap * LOG2E;
+        float m_ref = -INFINITY, l = 0.0f;                  // l: the sum over this thread's columns only
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int s = j & 1;
             ok = mbar_wait(bar(S_FULL + s), (j >> 1) & 1, give_up, 8);
             if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t sv[2][32];
-            tmem_ld32(tmem + lane_addr + S_COL + s * BN, sv[0]);
-            tmem_ld32(tmem + lane_addr + S_COL + s * BN + 32, sv[1]);
+            uint32_t sv[32];
+            tmem_ld32(tmem + lane_addr + S_COL + s * BN + half * 32, sv);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -300,76 +303,102 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
 
             const int key_base = (t_first + j) * BN;
             const bool edge = key_base + BN - 1 > tok0 || key_base < tok_hi - window + 1;
-            float sc[64];
+            // score in log2 units: with the cap,  cap log2e tanh(x) = c1 - c2 / (1 + 2^(s c0));  without,  s c0
+            float sc[32];
             float m_t = -INFINITY;
+            if (a.cap > 0.0f) {
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                float v = score_of(__uint_as_float(sv[c >> 5][c & 31]), a.scale, a.cap, inv_cap);
-                if (edge) {
-                    const int kp = key_base + c;
-                    if (!(row_ok && kp <= pos && pos - kp < window)) v = -INFINITY;
+                for (int c = 0; c < 32; ++c) {
+                    const float t = fast_exp2(__uint_as_float(sv[c]) * c0);
+                    sc[c] = fmaf(-c2, fast_rcp(1.0f + t), c1);
                 }
-                sc[c] = v;
-                m_t = fmaxf(m_t, v);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) sc[c] = __uint_as_float(sv[c]) * c0;
             }
+            if (edge) {
+                const int kp0 = key_base + half * 32;
+                // visible: kp <= pos and pos - kp < window, i.e. lo <= c <= hi for column c of this thread
+                const int hi = row_ok ? pos - kp0 : -1, lo = pos - window + 1 - kp0;
+#pragma unroll
+                for (int c = 0; c < 32; ++c)
+                    if (c > hi || c < lo) sc[c] = -INFINITY;
+            }
+#pragma unroll
+            for (int c = 0; c < 32; ++c) m_t = fmaxf(m_t, sc[c]);
+            float* slot = xch + (s * 2 + half) * BM + r;    // double-buffered by the tile's parity
+            *slot = m_t;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+            m_t = fmaxf(m_t, xch[(s * 2 + (half ^ 1)) * BM + r]);
             // raise the reference only when the tile goes well beyond it
             const bool raise = m_t > m_ref + RESCALE_GAP;       // also true for the first visible tile of a row
             const float m_new = raise ? m_t : m_ref;
             const float corr = (raise && m_ref > -INFINITY) ? fast_exp2(m_ref - m_new) : 1.0f;
 
-            if (j > 0) {
-                ok = mbar_wait(bar(PV_DONE), (j - 1) & 1, give_up, 10);     // P is free again and O is at rest
+            if (j >= 2) {
+                // the product that read this buffer of P two tiles ago is done
+                ok = mbar_wait(bar(PV_DONE + s), ((j - 2) >> 1) & 1, give_up, 10);
+                if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+            }
+            if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+                // rare: the accumulator has to be at rest (the product of the tile before is done), then every
+                // row of the warp is rescaled (rows that keep their reference multiply by 1); each warp of the
+                // pair takes half of the head size
+                ok = mbar_wait(bar(PV_DONE + (s ^ 1)), ((j - 1) >> 1) & 1, give_up, 12);
                 if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
-                    for (int c = 0; c < HD; c += 32) {
-                        uint32_t ov[32];
-                        tmem_ld32(tmem + lane_addr + O_COL + c, ov);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
+                    uint32_t ov[32];
+                    tmem_ld32(tmem + lane_addr + O_COL + c, ov);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
-                        tmem_st32(tmem + lane_addr + O_COL + c, ov);
-                    }
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                    tmem_st32(tmem + lane_addr + O_COL + c, ov);
                 }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
             l *= corr;
             m_ref = m_new;
             // probabilities -> shared memory, bfloat16, row r of a K-major tile with 128-byte swizzle
             float sum = 0.0f;
-            const uint32_t prow = p_s + r * 128;
+            const float m_sub = m_ref > -INFINITY ? m_ref : 0.0f;     // a row that has seen nothing: 2^(-inf - 0) = 0
+            const uint32_t prow = p_s + s * P_BYTES + r * 128;
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
+            for (int ch = 0; ch < 4; ++ch) {
                 uint32_t w[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float p0 = m_ref > -INFINITY ? fast_exp2(sc[ch * 8 + 2 * e] - m_ref) : 0.0f;
-                    const float p1 = m_ref > -INFINITY ? fast_exp2(sc[ch * 8 + 2 * e + 1] - m_ref) : 0.0f;
+                    const float p0 = fast_exp2(sc[ch * 8 + 2 * e] - m_sub), p1 = fast_exp2(sc[ch * 8 + 2 * e + 1] - m_sub);
                     sum += p0 + p1;
                     __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
                     w[e] = *reinterpret_cast<uint32_t*>(&t);
                 }
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + ((ch ^ (r & 7)) << 4)), "r"(w[0]),
-                             "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + (((half * 4 + ch) ^ (r & 7)) << 4)),
+                             "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
             }
             l += sum;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the tensor core reads P through the async proxy
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(P_FULL));
+            if (lane == 0) mbar_arrive(bar(P_FULL + s));
         }
         if (ok) {
-            ok = mbar_wait(bar(PV_DONE), (n_tiles - 1) & 1, give_up, 11);
+            ok = mbar_wait(bar(PV_DONE + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, give_up, 11);
             ok = __all_sync(0xffffffffu, ok);
         }
+        // the row's sum is the sum of the two halves (always added in the same order)
+        const int fin = (n_tiles & 1) * 2;                  // the buffer the next tile would have used
+        xch[(fin + half) * BM + r] = l;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            const float total = xch[fin * BM + r] + xch[(fin + 1) * BM + r];
+            const float inv = total > 0.0f ? 1.0f / total : 0.0f;
             const int row = row0 + r, tok = row / a.group, head = g * a.group + row % a.group;
             bf16* dst = a.out + (size_t)(q0 + tok) * a.out_stride + (size_t)head * HD;
 #pragma unroll 1
-            for (int c = 0; c < HD; c += 32) {
+            for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
                 uint32_t ov[32];
                 tmem_ld32(tmem + lane_addr + O_COL + c, ov);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -426,7 +455,7 @@ int make_map(CUtensorMap* map, const void* ptr, long long tokens, int heads, int
 template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcArgs& a, dim3 grid,
            cudaStream_t stream) {
-    constexpr size_t smem = 1024 + (size_t)BM * HD * 2 + 4 * (size_t)BN * HD * 2 + (size_t)BM * BN * 2 + N_BARS * 8 + 16;
+    constexpr size_t smem = (size_t)BM * HD * 2 + 4 * (size_t)BN * HD * 2 + 2 * (size_t)BM * BN * 2 + N_BARS * 8 + 16 + 4 * BM * 4;
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
