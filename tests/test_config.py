@@ -76,3 +76,28 @@ def test_layout_follows_the_configuration():
     assert [b.mixer.args["window"] for b in lay.blocks] == [16, None, 16]
     assert lay.blocks[0].mixer.args["scale"] == 24 ** -0.5 and lay.head.softcap == 15.0
     assert lay.embedding.scale == pytest.approx(96 ** 0.5)
+
+
+def test_absent_and_null_keys_read_as_in_the_reference(tmp_path):
+    """The same document through wlejon/brolm's own JSON reader (tests/golden/json_defaults.cpp) and
+    through Gemma2Config: absent and null keys give the defaults, present ones their values."""
+    import os
+    import shutil
+    import subprocess
+    here = os.path.dirname(os.path.abspath(__file__))
+    expected = open(os.path.join(here, "golden", "json_defaults.expected")).read()
+    ref_include = "/root/reference/include"
+    if shutil.which("g++") and os.path.exists(os.path.join(ref_include, "brolm", "detail", "json.h")):
+        exe = str(tmp_path / "json_defaults")
+        subprocess.check_call(["g++", "-std=c++20", "-I", ref_include, os.path.join(here, "golden", "json_defaults.cpp"),
+                               "-o", exe])
+        assert subprocess.check_output([exe], text=True) == expected      # the committed output is still the reader's
+    doc = ('{"hidden_size": 96, "head_dim": null, "rms_norm_eps": 1e-5, "tie_word_embeddings": false, '
+           '"vocab_size": 512.0, "rope_theta": null}')
+    c = bb.Gemma2Config.from_json_text(doc)
+    got = {"hidden_size": c.hidden_size, "head_dim": c.head_dim, "num_hidden_layers": c.num_hidden_layers,
+           "vocab_size": c.vocab_size, "tie_word_embeddings": int(c.tie_word_embeddings)}
+    want = dict(line.split() for line in expected.splitlines())
+    for key, value in got.items():
+        assert int(want[key]) == value, key
+    assert abs(float(want["rms_norm_eps"]) - c.rms_norm_eps) < 1e-12 and float(want["rope_theta"]) == c.rope_theta
