@@ -111,7 +111,7 @@ def test_forward_is_causal_and_bounded():
     assert plain.layer_is_sliding({**cfg, "layer_types": ["full_attention", "sliding_attention"]}, 1)
     gen = plain.greedy(cfg, w, ids[:3], 4)
     assert len(gen) == 4 and gen[0] == int(torch.argmax(plain.forward(cfg, w, ids[:3])[-1]))
-    assert plain.greedy(cfg, w, ids[:3], 4, stop_ids=(gen[1],)) == gen[:1]
+    assert plain.greedy(cfg, w, ids[:3], 4, stop_ids=(gen[2],)) == gen[:gen.index(gen[2])]
 
 
 def test_sampler_oracle():
