@@ -3,6 +3,8 @@ whole requests, the last 32 tokens one by one, batches of unequal lengths
 whose shorter requests end earlier (batch after batch, so that slots and pages
 are used again), long decoding past the window's ring, the first tokens of a
 sequence, and greedy generation through the entry point."""
+import os
+
 import pytest
 import torch
 
@@ -180,3 +182,58 @@ def test_step_refuses_a_mixed_batch(setups):
     with pytest.raises(bb.StepError):
         eng.step([b], [[config["vocab_size"]]])
     eng.close([a, b])
+
+
+ODD = dict(vocab_size=257, hidden_size=100, intermediate_size=90, num_hidden_layers=2, num_attention_heads=5,
+           num_key_value_heads=5, head_dim=48, rope_theta=5000.0, sliding_window=70, attn_logit_softcapping=0.0,
+           final_logit_softcapping=0.0, query_pre_attn_scalar=48, rms_norm_eps=1e-6, max_position_embeddings=256)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_fit_no_fast_path(tmp_path, dtype):
+    """A width that is no multiple of 8, an odd vocabulary, five heads of 48, no soft-caps at all, and a
+    window that is no multiple of the page: every kernel has to take its general path or hand over."""
+    folder = str(tmp_path / "odd")
+    bb.write_random_model(bb.Gemma2Config(**ODD), folder, seed=5, weight_std=0.05, dtype=STORE[dtype])
+    config, weights = oracle_inputs(folder)
+    model = bb.load_model(folder, dtype=dtype, device=DEV)
+    eng = bb.Engine(model, max_tokens=1024, max_slots=3)
+    prompts = random_prompts(257, [150, 20, 71], seed=6)
+    refs = [plain.forward(config, weights, p) for p in prompts]
+    pre = [140, 1, 70]
+    slots = eng.open(3)
+    got = eng.step(slots, [p[:k] for p, k in zip(prompts, pre)], want=[list(range(k)) for k in pre])
+    off = 0
+    for r, k in zip(refs, pre):
+        check(got[off:off + k], r[:k], dtype, "prompt")
+        off += k
+    for step in range(10):
+        live = [i for i in range(3) if pre[i] + step < len(prompts[i])]
+        got = eng.step([slots[i] for i in live], [[prompts[i][pre[i] + step]] for i in live])
+        for row, i in enumerate(live):
+            check(got[row], refs[i][pre[i] + step], dtype, f"decode {step} of request {i}")
+    eng.close(slots)
+
+
+def test_tensors_stored_in_32_bits_stay_so_and_still_compute(tmp_path):
+    """bfloat16 run of a checkpoint in which some gains and one matrix are stored as float32."""
+    from safetensors.torch import load_file, save_file
+    folder = make_folder(tmp_path, "B", torch.bfloat16)
+    path = os.path.join(folder, "model.safetensors")
+    tensors = load_file(path)
+    for name in ("model.layers.0.post_attention_layernorm.weight", "model.norm.weight",
+                 "model.layers.1.mlp.down_proj.weight", "model.layers.2.self_attn.k_proj.weight"):
+        tensors[name] = tensors[name].float()
+    save_file(tensors, path)
+    config, weights = oracle_inputs(folder)
+    model = bb.load_model(folder, dtype="bfloat16", device=DEV)
+    assert model.final_norm.weight.dtype == torch.float32 and model.blocks[1].feedforward.w_down.dtype == torch.float32
+    assert model.blocks[2].mixer.w_qkv.dtype == torch.float32 and model.blocks[0].mixer.w_qkv.dtype == torch.bfloat16
+    eng = bb.Engine(model, max_tokens=512)
+    p = random_prompts(config["vocab_size"], [90], seed=8)[0]
+    ref = plain.forward(config, weights, p)
+    (s,) = eng.open(1)
+    check(eng.step([s], [p[:80]], want=[list(range(80))]), ref[:80], "bfloat16", "prompt")
+    for i in range(80, 90):
+        check(eng.step([s], [[p[i]]])[0], ref[i], "bfloat16", f"token {i}")
+    eng.close([s])
