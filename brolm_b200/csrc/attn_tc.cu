@@ -31,16 +31,13 @@
 // Every mbarrier wait is bounded; a wait that runs out records a code that
 // brolm_attn_tc_status() returns, lets outstanding loads land, frees the tensor
 // memory and returns (the launch's results are then not valid).
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 namespace {
 
 constexpr int BM = 128, BN = 64;
 constexpr int THREADS = 320;      // loader warp, issuer warp, eight softmax warps
 constexpr int TMEM_COLS = 512;
-constexpr long long WAIT_CYCLES = 2000000000ll;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_GAP = 8.0f;
 
@@ -56,89 +53,13 @@ struct TcArgs {
     uint32_t v_lbo, v_sbo;      // descriptor strides of the value operand, in 16-byte units
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+using namespace tc;
+
+__device__ __forceinline__ bool wait_on(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
+    return mbar_wait(bar, parity, give_up, &g_attn_tc_error, code);
 }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (true) {
-        if (mbar_try(bar, parity)) return true;
-        if (*give_up) return false;
-        if (clock64() - t0 > WAIT_CYCLES) {
-            *give_up = 1;
-            atomicCAS(&g_attn_tc_error, 0, code);
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
-}
-// K-major operand: rows of 128 bytes, 128-byte swizzle, eight-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
-    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-// MN-major operand (the values: 64 head-size elements contiguous, keys strided), 128-byte swizzle.
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)(lbo & 0x3fffu) << 16) | ((uint64_t)(sbo & 0x3fffu) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-__device__ __forceinline__ uint32_t idesc(int m, int n, int b_mn_major) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
-           ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t id, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(id), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
-          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
-          "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
-          "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory");
-}
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ float fast_rcp(float x) {
-    float y;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
+__device__ __forceinline__ uint32_t idesc(int m, int n, int b_mn_major) { return idesc_bf16(m, n, b_mn_major); }
+
 // barrier slots
 enum : int { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13,
              PV_DONE = 15, N_BARS = 17 };
@@ -195,16 +116,14 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
         }
         give_up[0] = 0;
         give_up[1] = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_init_fence();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    fence_before_sync();
     __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 0) {
@@ -218,13 +137,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
                 const int s = j & 1;
                 const uint32_t ph = (j >> 1) & 1;
                 const int key0 = q0 + (t_first + j) * BN;
-                ok = mbar_wait(bar(K_EMPTY + s), ph ^ 1, give_up, 1);
+                ok = wait_on(bar(K_EMPTY + s), ph ^ 1, give_up, 1);
                 if (!ok) break;
                 mbar_expect_tx(bar(K_FULL + s), KV_BYTES);
                 for (int d = 0; d < DB; ++d)
                     tma_load_3d(k_s + s * KV_BYTES + d * (BN * 128), &map_k, d * 64, g, key0, bar(K_FULL + s));
                 ++issued_k;
-                ok = mbar_wait(bar(V_EMPTY + s), ph ^ 1, give_up, 2);
+                ok = wait_on(bar(V_EMPTY + s), ph ^ 1, give_up, 2);
                 if (!ok) break;
                 mbar_expect_tx(bar(V_FULL + s), KV_BYTES);
                 for (int d = 0; d < DB; ++d)
@@ -232,21 +151,21 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
                 ++issued_v;
             }
             if (*give_up) {        // let the loads in flight land before the block goes away
-                mbar_wait(bar(Q_FULL), 0, give_up + 1, 9);
-                for (int j = max(0, issued_k - 2); j < issued_k; ++j) mbar_wait(bar(K_FULL + (j & 1)), (j >> 1) & 1, give_up + 1, 9);
-                for (int j = max(0, issued_v - 2); j < issued_v; ++j) mbar_wait(bar(V_FULL + (j & 1)), (j >> 1) & 1, give_up + 1, 9);
+                wait_on(bar(Q_FULL), 0, give_up + 1, 9);
+                for (int j = max(0, issued_k - 2); j < issued_k; ++j) wait_on(bar(K_FULL + (j & 1)), (j >> 1) & 1, give_up + 1, 9);
+                for (int j = max(0, issued_v - 2); j < issued_v; ++j) wait_on(bar(V_FULL + (j & 1)), (j >> 1) & 1, give_up + 1, 9);
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && n_tiles > 0) {
             const uint32_t id_qk = idesc(BM, BN, 0), id_pv = idesc(BM, HD, 1);
-            bool ok = mbar_wait(bar(Q_FULL), 0, give_up, 3);
+            bool ok = wait_on(bar(Q_FULL), 0, give_up, 3);
             auto issue_qk = [&](int j) -> bool {
                 const int s = j & 1;
                 const uint32_t ph = (j >> 1) & 1;
-                if (!mbar_wait(bar(K_FULL + s), ph, give_up, 4)) return false;
-                if (!mbar_wait(bar(S_EMPTY + s), ph ^ 1, give_up, 5)) return false;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (!wait_on(bar(K_FULL + s), ph, give_up, 4)) return false;
+                if (!wait_on(bar(S_EMPTY + s), ph ^ 1, give_up, 5)) return false;
+                fence_after_sync();
 #pragma unroll
                 for (int d = 0; d < DB; ++d) {
                     const uint64_t qa = desc_kmajor(q_s + d * (BM * 128)), kb = desc_kmajor(k_s + s * KV_BYTES + d * (BN * 128));
@@ -262,9 +181,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles) { ok = issue_qk(j + 1); if (!ok) break; }
                 const int s = j & 1;
-                ok = mbar_wait(bar(P_FULL + s), (j >> 1) & 1, give_up, 6) && mbar_wait(bar(V_FULL + s), (j >> 1) & 1, give_up, 7);
+                ok = wait_on(bar(P_FULL + s), (j >> 1) & 1, give_up, 6) && wait_on(bar(V_FULL + s), (j >> 1) & 1, give_up, 7);
                 if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                fence_after_sync();
                 const uint64_t pa = desc_kmajor(p_s + s * P_BYTES);
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k) {
@@ -291,13 +210,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int s = j & 1;
-            ok = mbar_wait(bar(S_FULL + s), (j >> 1) & 1, give_up, 8);
+            ok = wait_on(bar(S_FULL + s), (j >> 1) & 1, give_up, 8);
             if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            fence_after_sync();
             uint32_t sv[32];
             tmem_ld32(tmem + lane_addr + S_COL + s * BN + half * 32, sv);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            tmem_wait_ld();
+            fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(S_EMPTY + s));
 
@@ -337,26 +256,26 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
 
             if (j >= 2) {
                 // the product that read this buffer of P two tiles ago is done
-                ok = mbar_wait(bar(PV_DONE + s), ((j - 2) >> 1) & 1, give_up, 10);
+                ok = wait_on(bar(PV_DONE + s), ((j - 2) >> 1) & 1, give_up, 10);
                 if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
             }
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
                 // rare: the accumulator has to be at rest (the product of the tile before is done), then every
                 // row of the warp is rescaled (rows that keep their reference multiply by 1); each warp of the
                 // pair takes half of the head size
-                ok = mbar_wait(bar(PV_DONE + (s ^ 1)), ((j - 1) >> 1) & 1, give_up, 12);
+                ok = wait_on(bar(PV_DONE + (s ^ 1)), ((j - 1) >> 1) & 1, give_up, 12);
                 if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                fence_after_sync();
 #pragma unroll 1
                 for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
                     uint32_t ov[32];
                     tmem_ld32(tmem + lane_addr + O_COL + c, ov);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
                     tmem_st32(tmem + lane_addr + O_COL + c, ov);
                 }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tmem_wait_st();
             }
             l *= corr;
             m_ref = m_new;
@@ -379,12 +298,12 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
             }
             l += sum;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the tensor core reads P through the async proxy
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(P_FULL + s));
         }
         if (ok) {
-            ok = mbar_wait(bar(PV_DONE + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, give_up, 11);
+            ok = wait_on(bar(PV_DONE + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, give_up, 11);
             ok = __all_sync(0xffffffffu, ok);
         }
         // the row's sum is the sum of the two halves (always added in the same order)
@@ -392,7 +311,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
         xch[(fin + half) * BM + r] = l;
         asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
         if (ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            fence_after_sync();
             const float total = xch[fin * BM + r] + xch[(fin + 1) * BM + r];
             const float inv = total > 0.0f ? 1.0f / total : 0.0f;
             const int row = row0 + r, tok = row / a.group, head = g * a.group + row % a.group;
@@ -401,7 +320,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
             for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
                 uint32_t ov[32];
                 tmem_ld32(tmem + lane_addr + O_COL + c, ov);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                tmem_wait_ld();
                 if (row_ok) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
@@ -416,40 +335,20 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
             }
         }
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    fence_before_sync();
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+        tmem_dealloc(tmem, TMEM_COLS);
     }
 }
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiled encoder() {
-    static EncodeTiled fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiled>(p);
-    }
-    return fn;
-}
 // [tokens][heads][hd] bfloat16 with `stride` elements between tokens; box = 64 x box_heads x box_tokens.
 int make_map(CUtensorMap* map, const void* ptr, long long tokens, int heads, int hd, long long stride, int box_heads,
              int box_tokens) {
-    EncodeTiled enc = encoder();
-    if (!enc) return BROLM_ERR_BAD_SIZE;
     const cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)heads, (cuuint64_t)tokens};
     const cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)stride * 2};
     const cuuint32_t box[3] = {64, (cuuint32_t)box_heads, (cuuint32_t)box_tokens};
-    const cuuint32_t elem[3] = {1, 1, 1};
-    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, elem,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? BROLM_OK : BROLM_ERR_ALIGNMENT;
+    return make_map_bf16(map, ptr, 3, dims, strides, box);
 }
 
 template <int HD>

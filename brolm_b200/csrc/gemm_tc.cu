@@ -27,9 +27,7 @@
 // error code that brolm_gemm_tc_status() returns, lets the loads in flight
 // land, frees the tensor memory and returns; results of that launch are then
 // not valid, the device stays usable.
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -37,7 +35,6 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;      // two accumulators of 256 columns
-constexpr long long WAIT_CYCLES = 2000000000ll;
 
 enum : int { EPI_STORE = 0, EPI_GATED = 1 };
 
@@ -52,86 +49,14 @@ struct GemmArgs {
     int m_tiles, n_tiles;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+using namespace tc;
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false when it gave up (its own limit, or another role's).
-__device__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (true) {
-        if (mbar_try(bar, parity)) return true;
-        if (*give_up) return false;
-        if (clock64() - t0 > WAIT_CYCLES) {
-            *give_up = 1;
-            atomicCAS(&g_gemm_tc_error, 0, code);
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-
-// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle, groups of
-// eight rows 1024 bytes apart (the layout the TMA loads above produce).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);        // start address
-    d |= (uint64_t)1 << 16;                             // leading byte offset (not used with this swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset
-    d |= (uint64_t)1 << 46;                             // descriptor version of sm_100
-    d |= (uint64_t)2 << 61;                             // 128-byte swizzle
-    return d;
-}
-// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M 128, N 256.
-__device__ __forceinline__ uint32_t umma_idesc() {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr) : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-// act(z) = z * sigmoid(k):  k = z for silu;  k = 2 sqrt(2/pi) (z + 0.044715 z^3) for the tanh form of gelu,
-// since 0.5 (1 + tanh(u)) = sigmoid(2u).  exp2 and the reciprocal are the hardware's approximations
-// (relative error about 1e-6, far below the bfloat16 the result is rounded to).
-__device__ __forceinline__ float act_apply(float z, int act) {
-    const float k = act == 0 ? 1.5957691216057308f * (z + 0.044715f * z * z * z) : z;
-    float e, r;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * k));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
-    return z * r;
+// Operand and instruction descriptors of this kernel's tile shapes.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) { return desc_kmajor(smem_addr); }
+__device__ __forceinline__ uint32_t umma_idesc() { return idesc_bf16(BM, BN); }
+__device__ __forceinline__ float act_apply(float z, int act) { return fast_gate_act(z, act); }
+__device__ __forceinline__ bool wait_on(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
+    return mbar_wait(bar, parity, give_up, &g_gemm_tc_error, code);
 }
 
 template <int EPI>
@@ -163,16 +88,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
         }
         give_up[0] = 0;
         give_up[1] = 0;      // the flag of the drain waits below
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_init_fence();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    fence_before_sync();
     __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 0) {
@@ -184,7 +107,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t phase = (it / STAGES) & 1;
-                    if (!mbar_wait(empty0 + 8 * s, phase ^ 1, give_up, 1)) { ok = false; break; }
+                    if (!wait_on(empty0 + 8 * s, phase ^ 1, give_up, 1)) { ok = false; break; }
                     const uint32_t full = full0 + 8 * s, a_dst = stage0 + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
                     mbar_expect_tx(full, STAGE_BYTES);
                     tma_load_2d(a_dst, &map_x, kb * BK, m_tile * BM, full);
@@ -199,7 +122,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
             if (*give_up) {
                 // let the loads that are still in flight land before the block goes away
                 for (int j = max(0, it - STAGES); j < it; ++j)
-                    mbar_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1, give_up + 1, 4);
+                    wait_on(full0 + 8 * (j % STAGES), (j / STAGES) & 1, give_up + 1, 4);
             }
         }
     } else if (warp == 1) {
@@ -209,15 +132,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
                 const int as = local & 1;                 // accumulator of this tile
-                ok = mbar_wait(acc_empty0 + 8 * as, ((local >> 1) & 1) ^ 1, give_up, 5);
+                ok = wait_on(acc_empty0 + 8 * as, ((local >> 1) & 1) ^ 1, give_up, 5);
                 if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                fence_after_sync();
                 const uint32_t acc = tmem + as * BN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
-                    ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, give_up, 2);
+                    ok = wait_on(full0 + 8 * s, (it / STAGES) & 1, give_up, 2);
                     if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    fence_after_sync();
                     const uint64_t a = umma_desc(stage0 + s * STAGE_BYTES), b = umma_desc(stage0 + s * STAGE_BYTES + A_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k)
@@ -233,9 +156,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
             const int m_tile = tile % g.m_tiles, n_tile = tile / g.m_tiles;
             const int as = local & 1;
-            const bool ready = mbar_wait(acc_full0 + 8 * as, (local >> 1) & 1, give_up, 3);
+            const bool ready = wait_on(acc_full0 + 8 * as, (local >> 1) & 1, give_up, 3);
             if (!__all_sync(0xffffffffu, ready)) break;       // the warp leaves together
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            fence_after_sync();
             const uint32_t acc = tmem + as * BN + ((uint32_t)(quarter * 32) << 16);
             const int row = m_tile * BM + quarter * 32 + lane;
             const int col0 = n_tile * OUT_COLS;
@@ -243,10 +166,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
                 uint32_t v[32], u[32];
                 tmem_ld32(acc + c, v);
                 if (EPI == EPI_GATED) tmem_ld32(acc + OUT_COLS + c, u);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                tmem_wait_ld();
                 if (c + 32 >= OUT_COLS) {
                     // everything of this accumulator is in registers: hand it back before the stores
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(acc_empty0 + 8 * as);
                 }
@@ -287,41 +210,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
             }
         }
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    fence_before_sync();
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+        tmem_dealloc(tmem, TMEM_COLS);
     }
 }
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encoder() {
-    static EncodeTiled fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiled>(p);
-    }
-    return fn;
-}
-
-// rows x cols bfloat16, row-major with `ld` elements between rows; box = box_rows x 64 columns.
 int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
-    EncodeTiled enc = encoder();
-    if (!enc) return BROLM_ERR_BAD_SIZE;
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? BROLM_OK : BROLM_ERR_ALIGNMENT;
+    return make_map_2d(map, ptr, rows, cols, ld, box_rows);
 }
 
 constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16;
@@ -329,12 +226,7 @@ constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES 
 template <int EPI>
 int launch(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& g, cudaStream_t stream) {
     static bool raised = false;
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
+    const int sms = device_sms();
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;

@@ -159,9 +159,10 @@ class DecoderModel:
         head_in = torch.float32 if self.head.dtype == torch.float32 else self.dtype
         xf = self.final_norm.apply(h, head_in, rows=rows)
         cap = float(lay.head.softcap or 0.0)
-        if kernels.skinny_ok(xf, self.head):
+        if kernels.gemm_stream_ok(xf, self.head):
+            # the largest stream of weights of a decode step: the TMA ring into tcgen05, soft-cap in the epilogue
             logits = torch.empty((xf.shape[0], self.head.shape[0]), dtype=torch.float32, device=self.device)
-            kernels.skinny_gemm(xf, self.head, logits, "softcap" if cap > 0 else "store", cap=cap)
+            kernels.gemm_stream(xf, self.head, logits, "softcap" if cap > 0 else "store", cap=cap)
             return logits
         logits = linear(xf, self.head, out_dtype=torch.float32)
         if cap > 0:

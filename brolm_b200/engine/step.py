@@ -19,6 +19,7 @@ wlejon/brolm's forward/forward_last take one sequence at ``cache_len``
 from __future__ import annotations
 
 import dataclasses
+import gc
 from typing import Optional, Sequence
 
 import numpy as np
@@ -54,7 +55,6 @@ class _DecodeGraph:
 
     def __init__(self, engine: "Engine", rows: int, kv_cap: int):
         cache, dev = engine.cache, engine.device
-        self.engine = engine
         self.rows, self.kv_cap = rows, kv_cap
         self.widths = []
         for g in cache.kv_groups:
@@ -96,8 +96,18 @@ class _DecodeGraph:
         self.copied.record()
         self.graph = torch.cuda.CUDAGraph()
         before = kernels.launch_count()
-        with torch.cuda.graph(self.graph, pool=engine._graph_pool):
-            self.logits = engine.model.forward(self.ctx, self.tokens, self.all_rows)
+        # Nothing may free device memory while the stream is capturing: objects that the collector
+        # would destroy in the middle of it (an older engine with graphs of its own) are collected now,
+        # and the collector stays off until the capture has ended.
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph, pool=engine._graph_pool):
+                self.logits = engine.model.forward(self.ctx, self.tokens, self.all_rows)
+        finally:
+            if was_enabled:
+                gc.enable()
         self.kernels = kernels.launch_count() - before      # this library's kernels in one replay
 
     def run(self, plan: _Plan, cache: Cache) -> torch.Tensor:
@@ -120,7 +130,6 @@ class _DecodeGraph:
             hv[off + g * R:off + g * R + B] = cache.write_rows(g, plan.slots, plan.old, plan.new_len)
         self.dev.copy_(self.host, non_blocking=True)
         self.copied.record()
-        self.engine.last_h2d_bytes = self.host.numel() * 4
         self.graph.replay()
         kernels.add_launches(self.kernels)
         return self.logits
@@ -163,7 +172,9 @@ class Engine:
         """
         plan = self._plan(slots, tokens, want)
         if plan.mode == "decode" and self.use_graphs:
-            logits = self._graph_for(plan).run(plan, self.cache)
+            graph = self._graph_for(plan)
+            logits = graph.run(plan, self.cache)
+            self.last_h2d_bytes = graph.host.numel() * 4
             if plan.rows != list(range(len(plan.slots))):
                 logits = logits[torch.tensor(plan.rows, dtype=torch.long, device=self.device)]
             else:
@@ -173,7 +184,8 @@ class Engine:
             logits = self.model.forward(ctx, tok_dev, rows)
             if plan.mode == "prefill" and self.model.dtype == torch.bfloat16 and self.device.type == "cuda":
                 # waits for the step; 0 unless a bounded wait inside a tcgen05 kernel ran out
-                code = kernels.gemm_tc_status(reset=True) or kernels.attention_tc_status(reset=True)
+                code = (kernels.gemm_tc_status(reset=True) or kernels.attention_tc_status(reset=True) or
+                        kernels.gemm_stream_status(reset=True))
                 if code:
                     raise StepError(f"step: a wait inside a tensor-core kernel ran out (code {code}); "
                                     f"the results of this step are not valid")

@@ -288,6 +288,60 @@ def gemm_tc_status(reset: bool = False) -> int:
     return f(1 if reset else 0)
 
 
+STREAM_MAX_ROWS = 128
+
+
+def gemm_stream_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether the tcgen05 weight-streaming product (few tokens) takes these operands."""
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and
+            0 < x.shape[0] <= STREAM_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(1) == 1 and
+            x.stride(0) % 8 == 0 and weight.stride(1) == 1 and weight.stride(0) % 8 == 0 and
+            x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def gemm_stream_parts(x: torch.Tensor, weight: torch.Tensor, sms: int = 148) -> int:
+    """Slices of K so that every SM gets a (128-row tile, slice) item of the weight stream."""
+    row_tiles = (weight.shape[0] + 127) // 128
+    nkb = (x.shape[1] + 63) // 64
+    want = max(1, sms // row_tiles)
+    per = max(2, (nkb + want - 1) // want)
+    return max(1, (nkb + per - 1) // per)
+
+
+def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "store",
+                activation: str = "gelu_tanh", cap: float = 0.0) -> None:
+    """out = x @ weight^T for at most 128 rows of x on tcgen05, the weights streamed through a TMA ring.
+
+    ``epilogue``: "store" (out bfloat16 or float32, or [parts, M, N] float32 partial sums of K slices),
+    "gated" (weight = [Wg; Wu], out = act(x Wg^T) * (x Wu^T), width a multiple of 64), "softcap" (float32)."""
+    assert gemm_stream_ok(x, weight) and out.stride(-1) == 1 and out.shape[-2] == x.shape[0]
+    M, K = x.shape
+    code = {"store": 0, "gated": 1, "softcap": 2}[epilogue]
+    N = out.shape[-1]
+    assert weight.shape == ((2 * N if code == 1 else N), K)
+    ksplit, part_stride = 1, 0
+    if out.dim() == 3:
+        assert code == 0 and out.dtype == torch.float32 and out.stride(1) == N
+        ksplit, part_stride = out.shape[0], out.stride(0)
+    if code == 2:
+        assert out.dtype == torch.float32
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"gemm_stream: unknown activation '{activation}'")
+    f = _fn("gemm_stream", "brolm_gemm_stream", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                                 c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(-2), M, N, K, code,
+             1 if out.dtype == torch.float32 else 0, ACTIVATIONS[activation], cap, ksplit, part_stride, _stream()),
+           "gemm_stream")
+
+
+def gemm_stream_status(reset: bool = False) -> int:
+    """0 if no bounded wait inside gemm_stream ever ran out; otherwise its code.  Synchronises."""
+    f = load_library("gemm_stream").brolm_gemm_stream_status
+    f.argtypes = [c_int]
+    f.restype = c_int
+    return f(1 if reset else 0)
+
+
 def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor, *, n_kv: int,
                    group: int, head_dim: int, scale: float, cap: float, window: int, batch: int, max_q_len: int,
                    k: Optional[torch.Tensor] = None, v: Optional[torch.Tensor] = None,
@@ -415,5 +469,6 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
 
 
 __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "embed_scale", "rmsnorm", "residual_rmsnorm",
-           "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_tc_status", "attention_decode_mma",
+           "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts",
+           "gemm_stream_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_tc_status", "attention_decode_mma",
            "decode_splits", "argmax", "sample"]

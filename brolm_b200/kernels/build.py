@@ -38,9 +38,10 @@ LIBRARIES: dict[str, list[str]] = {
     "attn_noalloc": ["attn_decode_noalloc.cu"],
     "gemm_tc": ["gemm_tc.cu"],
     "attn_tc": ["attn_tc.cu"],
+    "gemm_stream": ["gemm_stream.cu"],
     "sampling": ["sampling.cu"],
 }
-HEADERS = ["common.cuh", "attn_mma.cuh", "attn_decode_noalloc.h"]
+HEADERS = ["common.cuh", "attn_mma.cuh", "attn_decode_noalloc.h", "tcgen05.cuh"]
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

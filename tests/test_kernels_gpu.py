@@ -204,6 +204,46 @@ def test_gemm_tc_gated(M, F, K, act):
     assert kernels.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K,parts", [(1, 128, 256, 1), (8, 2304, 2048, 8), (16, 300, 200, 1), (17, 4096, 2304, 1),
+                                         (64, 2304, 9216, 8), (128, 512, 512, 3), (33, 1000, 72, 1)])
+def test_gemm_stream(M, N, K, parts):
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    ref = x.double() @ w.double().t()
+    for dt in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N), 7.0, dtype=dt, device=DEV)
+        kernels.gemm_stream(x, w, out)
+        close(out, ref, dt, scale=float(ref.abs().max()) * (50 if dt == torch.float32 else 1))
+    if parts > 1:
+        nkb = (K + 63) // 64
+        per = (nkb + parts - 1) // parts
+        parts = (nkb + per - 1) // per                      # no empty slice
+        y = torch.full((parts, M, N), float("nan"), dtype=torch.float32, device=DEV)
+        kernels.gemm_stream(x, w, y)
+        close(y.sum(0), ref, torch.float32, scale=float(ref.abs().max()) * 50)
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    kernels.gemm_stream(x, w, out, "softcap", cap=3.0)
+    close(out, plain.soft_cap(ref, 3.0), torch.float32, scale=3.0 * 50)
+    assert kernels.gemm_stream_status() == 0
+
+
+@pytest.mark.parametrize("M,F,K,act", [(1, 64, 64, "gelu_tanh"), (8, 9216, 2304, "gelu_tanh"), (50, 128, 72, "silu"),
+                                       (100, 320, 128, "gelu_tanh")])
+def test_gemm_stream_gated(M, F, K, act):
+    g = torch.Generator().manual_seed(F + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * F, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    out = torch.empty(M, F, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_stream(x, w, out, "gated", act)
+    gate, up = x.double() @ w[:F].double().t(), x.double() @ w[F:].double().t()
+    ref = (plain.gelu_tanh(gate) if act == "gelu_tanh" else gate * torch.sigmoid(gate)) * up
+    close(out, ref, torch.bfloat16)
+    assert kernels.gemm_stream_status() == 0
+    assert kernels.gemm_stream_parts(torch.empty(8, 2048), torch.empty(2304, 2048)) == 8
+    assert kernels.gemm_stream_parts(torch.empty(8, 2304), torch.empty(256000, 2304)) == 1
+
+
 def test_gemm_tc_strided_views():
     g = torch.Generator().manual_seed(2)
     big = torch.randn(40, 3 * 64, generator=g).to(torch.bfloat16).to(DEV)

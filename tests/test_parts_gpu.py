@@ -87,10 +87,13 @@ def test_attention_part_prompt_then_decode(dtype, window):
     ctx = make_ctx(cache, "prefill", [0, 0], lengths, dtype)
     y = att.forward(torch.cat([x[:n] for x, n in zip(xs, lengths)]).to(DEV), ctx, cache.entries[0])
     assert y.dtype == torch.float32
+    if y.dim() == 3:            # partial sums along K, which the residual kernel would add
+        y = y.sum(0)
     assert rel(y[:90], refs[0][:90]) <= TOL[dtype] and rel(y[90:], refs[1][:3]) <= TOL[dtype]
     for step in range(2):
         ctx = make_ctx(cache, "decode", [n + step for n in lengths], [1, 1], dtype)
         y = att.forward(torch.stack([x[n + step] for x, n in zip(xs, lengths)]).to(DEV), ctx, cache.entries[0])
+        y = y.sum(0) if y.dim() == 3 else y
         for b in range(2):
             assert rel(y[b], refs[b][lengths[b] + step]) <= TOL[dtype]
 
@@ -108,6 +111,7 @@ def test_feed_forward_part(dtype):
     ctx = Ctx()
     ctx.dtype = dtype
     y = ffn.forward(x.to(DEV), ctx)
+    y = y.sum(0) if y.dim() == 3 else y
     assert rel(y, plain.feed_forward(x, ws["gate"], ws["up"], ws["down"])) <= TOL[dtype]
 
 
