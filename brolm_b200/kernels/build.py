@@ -59,19 +59,29 @@ def _nvcc() -> str:
                            "the CUDA kernels of brolm_b200 cannot be built and there is no other path")
 
 
+_build_dir_cache: dict[str, str] = {}
+_dir_lock = threading.Lock()
+
+
 def _build_dir() -> str:
+    """The folder for built libraries, decided once per wanted path (the write
+    probe must not race with itself when several libraries build at a time)."""
     want = os.environ.get("BROLM_BUILD_DIR") or os.path.join(CSRC, "_build")
-    try:
-        os.makedirs(want, exist_ok=True)
-        probe = os.path.join(want, f".w{os.getpid()}")
-        with open(probe, "w"):
-            pass
-        os.remove(probe)
-        return want
-    except OSError:
-        alt = os.path.join(tempfile.gettempdir(), f"brolm_b200_build_{os.getuid()}")
-        os.makedirs(alt, exist_ok=True)
-        return alt
+    with _dir_lock:
+        got = _build_dir_cache.get(want)
+        if got is not None:
+            return got
+        try:
+            os.makedirs(want, exist_ok=True)
+            fd, probe = tempfile.mkstemp(prefix=".w", dir=want)
+            os.close(fd)
+            os.remove(probe)
+            got = want
+        except OSError:
+            got = os.path.join(tempfile.gettempdir(), f"brolm_b200_build_{os.getuid()}")
+            os.makedirs(got, exist_ok=True)
+        _build_dir_cache[want] = got
+        return got
 
 
 def _digest(name: str) -> str:
@@ -145,7 +155,21 @@ def build_all(verbose: bool = True) -> list[str]:
     for n in names:
         if isinstance(results[n], Exception):
             raise results[n]
-    return [str(results[n]) for n in names]
+    paths = [str(results[n]) for n in names]
+    _prune(paths)
+    return paths
+
+
+def _prune(keep: list[str]) -> None:
+    """Remove libraries of earlier source versions from the build folder."""
+    folder = _build_dir()
+    wanted = {os.path.basename(p) for p in keep}
+    for f in os.listdir(folder):
+        if f.startswith("libbrolm_") and f.endswith(".so") and f not in wanted:
+            try:
+                os.remove(os.path.join(folder, f))
+            except OSError:
+                pass
 
 
 def load_library(name: str) -> ctypes.CDLL:
