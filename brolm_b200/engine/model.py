@@ -8,6 +8,8 @@ final norm at the wanted rows, the output matrix and the soft-cap
 """
 from __future__ import annotations
 
+import weakref
+
 from typing import Optional
 
 import torch
@@ -53,6 +55,8 @@ class DecoderModel:
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.loaded = False
+        self._chain_plans = weakref.WeakKeyDictionary()    # cache -> compiled decode step
+        self._chain_why: Optional[str] = None              # why there is none ("": there is one)
 
     # construction ---------------------------------------------------------
     def _build(self, spec: PartSpec) -> Part:
@@ -122,6 +126,8 @@ class DecoderModel:
         for part, names in self._tensor_names:
             part.bind({local: tensors[ck] for local, ck in names.items() if local in part.param_specs()})
         self.loaded = True
+        self._chain_plans.clear()
+        self._chain_why = None
 
     # cache ----------------------------------------------------------------
     def cache_specs(self) -> list:
@@ -139,10 +145,29 @@ class DecoderModel:
         return cache
 
     # the pass -------------------------------------------------------------
+    def _decode_chains(self, ctx):
+        """The compiled form of a decode step of few tokens (engine/fused.py), or None when the
+        step runs part by part: a prefill, more tokens than a chain takes, parts it does not know."""
+        from . import fused
+        if ctx.mode != "decode" or ctx.n_tokens > fused.ROWS or ctx.n_tokens != ctx.batch:
+            return None
+        if self._chain_why is None:
+            self._chain_why = fused.supported(self) or ""
+        if self._chain_why:
+            return None
+        key = ctx.cache
+        plan = self._chain_plans.get(key)
+        if plan is None:
+            plan = self._chain_plans[key] = fused.DecodeChains(self, ctx.cache)
+        return plan
+
     def forward(self, ctx, tokens: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """Run the packed ``tokens`` of a step; logits (len(rows), vocab), float32."""
         if not self.loaded:
             raise RuntimeError("forward: weights not loaded")
+        chains = self._decode_chains(ctx)
+        if chains is not None:
+            return chains.run(ctx, tokens, rows)
         lay = self.layout
         h = torch.empty((ctx.n_tokens, lay.embedding.hidden), dtype=torch.float32, device=self.device)
         kernels.embed_scale(tokens, self.embedding, lay.embedding.scale, h)

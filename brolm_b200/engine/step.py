@@ -160,6 +160,12 @@ class Engine:
     def close(self, slots: Sequence[int]) -> None:
         for s in slots:
             self.cache.free_slot(s)
+        if self.device.type == "cuda":
+            code = kernels.decode_chain_status(reset=True)
+            if code:
+                self.model._chain_plans.clear()      # their barrier words are not zero any more
+                raise StepError(f"close: a wait inside the decode chain ran out (code {code}); the tokens "
+                                f"decoded for these sequences are not valid")
 
     # the step -------------------------------------------------------------
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],

@@ -342,6 +342,68 @@ def gemm_stream_status(reset: bool = False) -> int:
     return f(1 if reset else 0)
 
 
+# ---------------------------------------------------------------------------
+# The decode chain: lists of operations run by one persistent kernel.
+CHAIN_MAX_TOKENS = 16
+CHAIN_OP_FIELDS = 32          # eight-byte fields of an operation
+CHAIN_MAP_BYTES = 128
+# field indices of an operation, as the kernel reads them
+CHAIN_FIELDS = {n: i for i, n in enumerate(
+    ["kind", "epi", "act", "map_w", "map_x", "N", "K", "ksplit", "per", "row_tiles", "items", "ldy", "part_stride",
+     "y", "cap", "h", "parts", "n_parts", "in_stride", "hidden", "w_post", "eps_post", "off_post", "w_next",
+     "eps_next", "off_next", "out", "cos_sin", "k_pages", "v_pages", "heads", "rope"])}
+CHAIN_GEMM, CHAIN_NORM, CHAIN_ROPE = 0, 1, 2
+CHAIN_PARTS, CHAIN_GATED, CHAIN_SOFTCAP = 0, 1, 2
+
+
+def chain_make_map(t: torch.Tensor, box_rows: int) -> bytes:
+    """The TMA descriptor (128 bytes) of a row-major bfloat16 matrix, boxes of box_rows x 64."""
+    assert t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1
+    buf = ctypes.create_string_buffer(CHAIN_MAP_BYTES)
+    f = _fn("decode_chain", "brolm_chain_make_map", [c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_int])
+    global _launches
+    _check(f(ctypes.addressof(buf), _ptr(t), t.shape[0], t.shape[1], t.stride(0), box_rows), "chain_make_map")
+    _launches -= 1                 # nothing ran on the device
+    return buf.raw
+
+
+def decode_chain(maps: torch.Tensor, ops: torch.Tensor, first: int, count: int, tokens: int,
+                 positions: torch.Tensor, cache_rows: list, sync: torch.Tensor,
+                 trace: Optional[torch.Tensor] = None) -> None:
+    """Run operations [first, first + count) of a chain for ``tokens`` rows (at most CHAIN_MAX_TOKENS).
+
+    ``maps``: uint8 [n, 128] tensor maps; ``ops``: int64 [n, 32]; ``sync``: four int32 words that were
+    zero before the first launch; ``cache_rows``: up to four int32 tensors, one per key/value group;
+    ``trace``: int64 [blocks, count, 8], filled with nanosecond stamps (start, work done, barrier passed,
+    first tile multiplied, last tile issued) for looking at where a chain's time goes."""
+    assert ops.dtype == torch.int64 and ops.shape[1] == CHAIN_OP_FIELDS and ops.is_contiguous()
+    assert maps.dtype == torch.uint8 and maps.is_contiguous() and sync.dtype == torch.int32 and sync.numel() >= 4
+    assert positions.dtype == torch.int32 and positions.numel() >= tokens and len(cache_rows) <= 4
+    rows = [_ptr(r) for r in cache_rows] + [None] * (4 - len(cache_rows))
+    global _chain_used
+    _chain_used = True
+    f = _fn("decode_chain", "brolm_decode_chain", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    if trace is not None:
+        assert trace.dtype == torch.int64 and trace.is_contiguous() and trace.numel() >= 148 * count * 8
+    _check(f(_ptr(maps), _ptr(ops), first, count, tokens, _ptr(positions), rows[0], rows[1], rows[2], rows[3],
+             _ptr(sync), _ptr(trace), _stream()), "decode_chain")
+
+
+_chain_used = False
+
+
+def decode_chain_status(reset: bool = False) -> int:
+    """0 if no bounded wait inside the decode chain ever ran out (or none ever ran); otherwise its code.
+    Synchronises."""
+    if not _chain_used:
+        return 0
+    f = load_library("decode_chain").brolm_decode_chain_status
+    f.argtypes = [c_int]
+    f.restype = c_int
+    return f(1 if reset else 0)
+
+
 def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor, *, n_kv: int,
                    group: int, head_dim: int, scale: float, cap: float, window: int, batch: int, max_q_len: int,
                    k: Optional[torch.Tensor] = None, v: Optional[torch.Tensor] = None,
@@ -470,5 +532,5 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
 
 __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "embed_scale", "rmsnorm", "residual_rmsnorm",
            "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts",
-           "gemm_stream_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_tc_status", "attention_decode_mma",
+           "gemm_stream_status", "chain_make_map", "decode_chain", "decode_chain_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_tc_status", "attention_decode_mma",
            "decode_splits", "argmax", "sample"]

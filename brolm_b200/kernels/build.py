@@ -39,6 +39,7 @@ LIBRARIES: dict[str, list[str]] = {
     "gemm_tc": ["gemm_tc.cu"],
     "attn_tc": ["attn_tc.cu"],
     "gemm_stream": ["gemm_stream.cu"],
+    "decode_chain": ["decode_chain.cu"],
     "sampling": ["sampling.cu"],
 }
 HEADERS = ["common.cuh", "attn_mma.cuh", "attn_decode_noalloc.h", "tcgen05.cuh"]
