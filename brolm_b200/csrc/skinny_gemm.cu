@@ -15,8 +15,12 @@
 // add their partial sums in shared memory in warp order (the result does not
 // depend on scheduling).  Epilogues: plain store (bfloat16 or float), the
 // gated activation act(gate) * up for W = [Wg; Wu] (wlejon/brolm
-// src/gemma2.cpp:378-381), or cap * tanh(y / cap) into float logits
-// (src/gemma2.cpp:406-412).
+// src/gemma2.cpp:378-381), cap * tanh(y / cap) into float logits
+// (src/gemma2.cpp:406-412), or, for the fused q/k/v projection, the rotary
+// position encoding of q and k with the write of k and v into the paged cache
+// (src/gemma2.cpp:355-356): a tile then holds eight (i, i + hd/2) pairs of one
+// head, rows i in its first eight rows and rows i + hd/2 in the other eight,
+// so that both elements of a pair meet in one thread.
 #include "common.cuh"
 
 namespace {
@@ -51,7 +55,7 @@ __device__ __forceinline__ float act_apply(float z, int act) {
     return z / (1.0f + expf(-z));
 }
 
-enum : int { EPI_STORE = 0, EPI_GATED = 1, EPI_SOFTCAP = 2 };
+enum : int { EPI_STORE = 0, EPI_GATED = 1, EPI_SOFTCAP = 2, EPI_ROPE = 3 };
 
 struct SkinnyArgs {
     const bf16* x;
@@ -64,6 +68,14 @@ struct SkinnyArgs {
     float cap;
     int ksplit;           // blocks along K; > 1: block (x, s) writes float partial sums to y + s * part_stride
     long long part_stride;
+    // EPI_ROPE: W = [Wq; Wk; Wv], heads of hd rows; y is the bfloat16 q/k/v row of a token
+    const int32_t* positions;     // < 0: a padding row, nothing is written for it
+    const float2* cos_sin;        // [position][hd / 2] (cos, sin); null: no rotation
+    int n_q, n_kv, hd;
+    bf16* k_pages;                // [page][kv head][page_size][hd]; null: nothing is kept
+    bf16* v_pages;
+    const int32_t* cache_rows;    // page * page_size + place of a token, < 0: not kept
+    int page_size;
 };
 
 // MT: 16-row tiles of W per block.  NT: 8-token tiles.
@@ -76,10 +88,19 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
     const int n0 = blockIdx.x * OUT_TILES * 16;
 
     // first row of W of each tile
+    // (EPI_ROPE: tile t of the grid is pairs 8j .. 8j + 7 of head h, t = h * (hd / 16) + j; its rows
+    // 8 .. 15 are the partners hd / 2 further on)
     int wrow[MT];
+    const int half = EPI == EPI_ROPE ? a.hd >> 1 : 8;
 #pragma unroll
-    for (int i = 0; i < MT; ++i)
-        wrow[i] = EPI == EPI_GATED ? ((i & 1) ? a.N : 0) + n0 + 16 * (i >> 1) : n0 + 16 * i;
+    for (int i = 0; i < MT; ++i) {
+        if (EPI == EPI_ROPE) {
+            const int t = blockIdx.x * MT + i, per_head = a.hd >> 4;
+            wrow[i] = (t / per_head) * a.hd + (t % per_head) * 8;
+        } else {
+            wrow[i] = EPI == EPI_GATED ? ((i & 1) ? a.N : 0) + n0 + 16 * (i >> 1) : n0 + 16 * i;
+        }
+    }
     const int w_rows = EPI == EPI_GATED ? 2 * a.N : a.N;
     const int n_limit = a.N;                                       // output columns that exist
 
@@ -103,7 +124,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
             for (int i = 0; i < MT; ++i) {
                 const int col = (EPI == EPI_GATED ? wrow[i] - ((i & 1) ? a.N : 0) : wrow[i]) + r;   // output column of row r
                 wv[h][i][0] = ldg16(a.w + (size_t)(wrow[i] + r) * a.ldw + kk, kok && col < n_limit);
-                wv[h][i][1] = ldg16(a.w + (size_t)(wrow[i] + r + 8) * a.ldw + kk, kok && col + 8 < n_limit);
+                wv[h][i][1] = ldg16(a.w + (size_t)(wrow[i] + r + half) * a.ldw + kk, kok && col + half < n_limit);
             }
         }
     };
@@ -165,6 +186,49 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
             for (int e = 0; e < 4; ++e) red[warp][(i * NT + j) * 4 + e][lane] = acc[i][j][e];
     __syncthreads();
 
+    if (EPI == EPI_ROPE) {
+        // one (pair, token) per thread and step: e & 1 picks the token, rows r and r + 8 are the pair
+        constexpr int PAIRS = MT * NT * 2 * 32;
+        for (int idx = threadIdx.x; idx < PAIRS; idx += WARPS * 32) {
+            const int ln = idx & 31, e = (idx >> 5) & 1, j = (idx >> 6) % NT, i = (idx >> 6) / NT;
+            const int tok = j * 8 + (ln & 3) * 2 + e;
+            const int col = wrow[i] + (ln >> 2);                    // first element of the pair in the q/k/v row
+            if (tok >= a.M || col >= n_limit) continue;
+            const int pos = a.positions[tok];
+            if (pos < 0) continue;
+            float va = 0.0f, vb = 0.0f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                va += red[w][(i * NT + j) * 4 + e][ln];
+                vb += red[w][(i * NT + j) * 4 + e + 2][ln];
+            }
+            const int head = col / a.hd, within = col - head * a.hd;
+            const bool is_v = head >= a.n_q + a.n_kv, is_k = !is_v && head >= a.n_q;
+            if (!is_v && a.cos_sin) {
+                const float2 c = a.cos_sin[(size_t)pos * half + within];
+                const float ra = va * c.x - vb * c.y, rb = va * c.y + vb * c.x;
+                va = ra;
+                vb = rb;
+            }
+            const bf16 qa = __float2bfloat16_rn(va), qb = __float2bfloat16_rn(vb);
+            bf16* y = reinterpret_cast<bf16*>(a.y) + (size_t)tok * a.ldy + col;
+            y[0] = qa;
+            y[half] = qb;
+            if ((is_k || is_v) && a.k_pages) {
+                const int crow = a.cache_rows[tok];
+                if (crow >= 0) {
+                    const int kvh = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
+                    bf16* dst = (is_k ? a.k_pages : a.v_pages) +
+                                (((size_t)(crow / a.page_size) * a.n_kv + kvh) * a.page_size + crow % a.page_size) * a.hd +
+                                within;
+                    dst[0] = qa;
+                    dst[half] = qb;
+                }
+            }
+        }
+        return;
+    }
+
     constexpr int OUT_ELEMS = OUT_TILES * NT * 4 * 32;
     for (int idx = threadIdx.x; idx < OUT_ELEMS; idx += WARPS * 32) {
         const int ln = idx & 31, e = (idx >> 5) & 3, j = (idx >> 7) % NT, ot = (idx >> 7) / NT;
@@ -196,19 +260,23 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
 template <int MT, int NT, int EPI>
 int launch(const SkinnyArgs& a, cudaStream_t stream) {
     constexpr int cols = (EPI == EPI_GATED ? MT / 2 : MT) * 16;
-    dim3 blocks((a.N + cols - 1) / cols, a.ksplit);
+    dim3 blocks((a.N + cols - 1) / cols, a.ksplit);        // (EPI_ROPE: hd is a multiple of 16, so N is too)
     return launch_pdl(skinny_kernel<MT, NT, EPI>, blocks, dim3(WARPS * 32), 0, stream, a);
 }
 
 template <int EPI>
 int dispatch(const SkinnyArgs& a, int mt, cudaStream_t stream) {
     const int nt = (a.M + 7) / 8;
-    if (EPI == EPI_GATED) {
+    if constexpr (EPI == EPI_GATED) {
         if (nt == 1) return mt >= 4 ? launch<4, 1, EPI>(a, stream) : launch<2, 1, EPI>(a, stream);
         return mt >= 4 ? launch<4, 2, EPI>(a, stream) : launch<2, 2, EPI>(a, stream);
+    } else if constexpr (EPI == EPI_ROPE) {
+        if (nt == 1) return mt >= 2 && (a.N / 16) % 2 == 0 ? launch<2, 1, EPI>(a, stream) : launch<1, 1, EPI>(a, stream);
+        return mt >= 2 && (a.N / 16) % 2 == 0 ? launch<2, 2, EPI>(a, stream) : launch<1, 2, EPI>(a, stream);
+    } else {
+        if (nt == 1) return mt >= 4 ? launch<4, 1, EPI>(a, stream) : mt >= 2 ? launch<2, 1, EPI>(a, stream) : launch<1, 1, EPI>(a, stream);
+        return mt >= 4 ? launch<4, 2, EPI>(a, stream) : mt >= 2 ? launch<2, 2, EPI>(a, stream) : launch<1, 2, EPI>(a, stream);
     }
-    if (nt == 1) return mt >= 4 ? launch<4, 1, EPI>(a, stream) : mt >= 2 ? launch<2, 1, EPI>(a, stream) : launch<1, 1, EPI>(a, stream);
-    return mt >= 4 ? launch<4, 2, EPI>(a, stream) : mt >= 2 ? launch<2, 2, EPI>(a, stream) : launch<1, 2, EPI>(a, stream);
 }
 
 }  // namespace
@@ -218,6 +286,31 @@ int dispatch(const SkinnyArgs& a, int mt, cudaStream_t stream) {
 // rows of X and W 16-byte aligned.  tiles: 16-row tiles of W per block (1, 2 or 4).
 // ksplit > 1 (epilogue 0 only): K is cut into ksplit slices, slice s writes its float partial
 // sums at y + s * part_stride (elements); the reader adds the slices in order.
+// The fused q/k/v projection of at most 16 tokens with the rotary position encoding and the write of
+// k and v into the paged cache as its epilogue.  W = [Wq; Wk; Wv] ((n_q + 2 n_kv) * hd rows, hd a
+// multiple of 16), y the bfloat16 q/k/v rows.  The rotation covers the whole head (pairs i, i + hd/2);
+// cos_sin null: no rotation; k_pages null: nothing is kept.
+BROLM_API int brolm_skinny_qkv_rope(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int M, int K,
+                                    const void* positions, const void* cos_sin, int n_q, int n_kv, int hd,
+                                    void* k_pages, void* v_pages, const void* cache_rows, int page_size, int tiles,
+                                    cudaStream_t stream) {
+    if (M <= 0) return BROLM_OK;
+    if (M > 16) return BROLM_ERR_TOO_LARGE;
+    if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return BROLM_ERR_ALIGNMENT;
+    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return BROLM_ERR_ALIGNMENT;
+    if (hd <= 0 || hd % 16 != 0 || n_q <= 0 || n_kv <= 0 || page_size <= 0) return BROLM_ERR_BAD_SIZE;
+    if (k_pages && (!v_pages || !cache_rows)) return BROLM_ERR_BAD_SIZE;
+    SkinnyArgs a;
+    a.x = (const bf16*)x; a.w = (const bf16*)w; a.y = y; a.ldx = ldx; a.ldw = ldw; a.ldy = ldy;
+    a.M = M; a.N = (n_q + 2 * n_kv) * hd; a.K = K; a.out_f32 = 0; a.act = 0; a.cap = 0.0f;
+    a.ksplit = 1; a.part_stride = 0;
+    a.positions = (const int32_t*)positions; a.cos_sin = (const float2*)cos_sin;
+    a.n_q = n_q; a.n_kv = n_kv; a.hd = hd;
+    a.k_pages = (bf16*)k_pages; a.v_pages = (bf16*)v_pages; a.cache_rows = (const int32_t*)cache_rows;
+    a.page_size = page_size;
+    return dispatch<EPI_ROPE>(a, tiles, stream);
+}
+
 BROLM_API int brolm_skinny_gemm(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int M, int N, int K,
                                 int epilogue, int out_f32, int act, float cap, int tiles, int ksplit,
                                 long long part_stride, cudaStream_t stream) {
@@ -231,6 +324,8 @@ BROLM_API int brolm_skinny_gemm(const void* x, int ldx, const void* w, int ldw, 
     a.M = M; a.N = N; a.K = K; a.out_f32 = out_f32; a.act = act; a.cap = cap;
     if (ksplit < 1 || ksplit > 64 || (ksplit > 1 && epilogue != EPI_STORE)) return BROLM_ERR_BAD_SIZE;
     a.ksplit = ksplit; a.part_stride = part_stride;
+    a.positions = nullptr; a.cos_sin = nullptr; a.n_q = a.n_kv = a.hd = 0; a.k_pages = a.v_pages = nullptr;
+    a.cache_rows = nullptr; a.page_size = 0;
     if (epilogue == EPI_STORE) return dispatch<EPI_STORE>(a, tiles, stream);
     if (epilogue == EPI_GATED) return dispatch<EPI_GATED>(a, tiles, stream);
     if (epilogue == EPI_SOFTCAP) { a.out_f32 = 1; return dispatch<EPI_SOFTCAP>(a, tiles, stream); }

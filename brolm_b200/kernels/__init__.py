@@ -246,6 +246,33 @@ def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilog
              _stream()), "skinny_gemm")
 
 
+def skinny_qkv_rope(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
+                    cos_sin: Optional[torch.Tensor], n_q: int, n_kv: int, head_dim: int,
+                    k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
+                    cache_rows: Optional[torch.Tensor] = None, page_size: int = 64) -> None:
+    """out = x @ [Wq; Wk; Wv]^T for at most 16 rows of x, with q and k rotated over the whole head
+    (pairs i, i + head_dim/2; ``cos_sin`` [positions, head_dim/2, 2], None: no rotation) and k, v written
+    into the cache pages as well: ``rope_kv_write`` as the epilogue of the product, one rounding to
+    bfloat16 instead of two.  Rows with a negative position are not written."""
+    assert skinny_ok(x, weight) and out.dtype == torch.bfloat16 and out.stride(1) == 1
+    width = (n_q + 2 * n_kv) * head_dim
+    assert weight.shape == (width, x.shape[1]) and out.shape == (x.shape[0], width) and head_dim % 16 == 0
+    assert positions.dtype == torch.int32 and positions.numel() == x.shape[0]
+    if cos_sin is not None:
+        assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] == head_dim // 2
+    if k_pages is not None:
+        assert v_pages is not None and cache_rows is not None and k_pages.dtype == torch.bfloat16
+        assert k_pages.is_contiguous() and v_pages.is_contiguous()
+        assert tuple(k_pages.shape[1:]) == (n_kv, page_size, head_dim)
+        assert cache_rows.dtype == torch.int32 and cache_rows.numel() == x.shape[0]
+    f = _fn("skinny_gemm", "brolm_skinny_qkv_rope", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                                     c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                                                     c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), x.shape[0], x.shape[1],
+             _ptr(positions), _ptr(cos_sin), n_q, n_kv, head_dim, _ptr(k_pages), _ptr(v_pages), _ptr(cache_rows),
+             page_size, 2 if width >= 32 * 296 else 1, _stream()), "skinny_qkv_rope")
+
+
 USE_TC_GEMM = True      # False: many-token bfloat16 products go to the library (cuBLAS) instead
 
 
@@ -531,6 +558,6 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
 
 
 __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "embed_scale", "rmsnorm", "residual_rmsnorm",
-           "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts",
+           "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts",
            "gemm_stream_status", "chain_make_map", "decode_chain", "decode_chain_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_tc_status", "attention_decode_mma",
            "decode_splits", "argmax", "sample"]

@@ -60,14 +60,18 @@ class Attention(Part):
     def forward(self, x: torch.Tensor, ctx, entry, writes_cache: bool = True) -> torch.Tensor:
         """x (tokens, hidden) in the step's element type -> (tokens, hidden) float32, or
         [parts, tokens, hidden] partial sums that the residual kernel adds."""
-        qkv = linear(x, self.w_qkv, out_dtype=ctx.dtype)
         k_pages, v_pages, table, ring, page = ctx.kv(entry)
         rot = self.position.rotary_dim if self.position is not None else 0
-        kernels.rope_kv_write(
-            qkv, ctx.positions, self.position.table if self.position is not None else None,
-            self.n_q, self.n_kv, self.head_dim, rot,
-            k_pages if writes_cache else None, v_pages if writes_cache else None,
-            ctx.cache_rows[entry.group_id] if writes_cache else None, page)
+        cos_sin = self.position.table if self.position is not None else None
+        kept = (k_pages, v_pages, ctx.cache_rows[entry.group_id]) if writes_cache else (None, None, None)
+        if kernels.skinny_ok(x, self.w_qkv) and (cos_sin is None or rot == self.head_dim):
+            # a few tokens: the rotation and the write into the cache are the product's epilogue
+            qkv = torch.empty((x.shape[0], self.q_dim + 2 * self.kv_dim), dtype=ctx.dtype, device=x.device)
+            kernels.skinny_qkv_rope(x, self.w_qkv, qkv, ctx.positions, cos_sin, self.n_q, self.n_kv, self.head_dim,
+                                    *kept, page)
+        else:
+            qkv = linear(x, self.w_qkv, out_dtype=ctx.dtype)
+            kernels.rope_kv_write(qkv, ctx.positions, cos_sin, self.n_q, self.n_kv, self.head_dim, rot, *kept, page)
         q = qkv[:, :self.q_dim]
         out = torch.empty((qkv.shape[0], self.q_dim), dtype=ctx.dtype, device=x.device)
         common = dict(n_kv=self.n_kv, group=self.n_q // self.n_kv, head_dim=self.head_dim, scale=self.scale,

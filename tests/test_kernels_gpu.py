@@ -542,3 +542,55 @@ def test_kernels_refuse_what_they_cannot_do():
         kernels.gated_act(torch.zeros(1, 8, device=DEV), torch.zeros(1, 4, device=DEV), "relu")
     with pytest.raises(kernels.KernelError):
         kernels.embed_scale(torch.zeros(1, dtype=torch.int32), torch.zeros(4, 4), 1.0, torch.zeros(1, 4))
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd,K,M", [(4, 2, 16, 64, 5), (6, 1, 32, 96, 3), (8, 4, 256, 2304, 8), (3, 1, 48, 72, 16),
+                                             (5, 5, 64, 136, 9)])
+def test_qkv_product_with_rotation_and_cache_write(n_q, n_kv, hd, K, M):
+    """The few-token q/k/v product whose epilogue rotates q and k and writes k, v into the pages:
+    against float64, with a padding row (nothing written) and a row that is not kept."""
+    from brolm_b200 import kernels
+    g = torch.Generator().manual_seed(hd * 7 + K)
+    width, page, pages, half = (n_q + 2 * n_kv) * hd, 64, 4, hd // 2
+    w = (torch.randn(width, K, generator=g) * 0.1).to(DEV).bfloat16()
+    x = torch.randn(M, K, generator=g).to(DEV).bfloat16()
+    pos_list = [3, 70, -1, 0, 129] + list(range(5, 16))
+    row_list = [3, 64 + 6, 9, -1, 2 * 64 + 1] + list(range(200, 211))
+    pos = torch.tensor(pos_list[:M], dtype=torch.int32, device=DEV)
+    crow = torch.tensor(row_list[:M], dtype=torch.int32, device=DEV)
+    ang = torch.arange(256, dtype=torch.float64)[:, None] * (10000.0 ** (-2.0 * torch.arange(half, dtype=torch.float64) / hd))
+    table = torch.stack([ang.cos(), ang.sin()], -1).float().to(DEV).contiguous()
+    for use_table, use_pages in ((True, True), (False, True), (True, False)):
+        out = torch.full((M, width), 7.0, dtype=torch.bfloat16, device=DEV)
+        k_pages = torch.zeros(pages, n_kv, page, hd, dtype=torch.bfloat16, device=DEV)
+        v_pages = torch.zeros_like(k_pages)
+        kernels.skinny_qkv_rope(x, w, out, pos, table if use_table else None, n_q, n_kv, hd,
+                                k_pages if use_pages else None, v_pages if use_pages else None,
+                                crow if use_pages else None, page)
+        src = (x.double() @ w.double().t()).view(M, n_q + 2 * n_kv, hd)
+        want = src.clone()
+        if use_table:
+            for t in range(M):
+                p = pos_list[t]
+                if p >= 0:
+                    c, s = table[p, :, 0].double(), table[p, :, 1].double()
+                    a, b = src[t, :n_q + n_kv, :half], src[t, :n_q + n_kv, half:]
+                    want[t, :n_q + n_kv, :half] = a * c - b * s
+                    want[t, :n_q + n_kv, half:] = a * s + b * c
+        got = out.double().view(M, n_q + 2 * n_kv, hd)
+        kept = set()
+        for t in range(M):
+            if pos_list[t] < 0:
+                assert (got[t] == 7.0).all()
+                continue
+            err = (got[t] - want[t]).abs()
+            assert (err <= 2.0 ** -8 * want[t].abs() + 1e-5 * want[t].abs().max()).all()      # one rounding
+            r = row_list[t]
+            if use_pages and r >= 0:
+                kept.add(r)
+                assert torch.equal(k_pages[r // page, :, r % page].double(), got[t, n_q:n_q + n_kv])
+                assert torch.equal(v_pages[r // page, :, r % page].double(), got[t, n_q + n_kv:])
+        mask = torch.ones(pages * page, dtype=torch.bool)
+        mask[list(kept)] = False
+        for pg in (k_pages, v_pages):
+            assert (pg.permute(0, 2, 1, 3).reshape(pages * page, -1)[mask.to(DEV)] == 0).all()
