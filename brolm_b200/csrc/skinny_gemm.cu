@@ -4,15 +4,18 @@
 // With so few tokens the product only has to stream W from memory once, so
 // the kernel is built around that stream.  The roles of the operands are
 // swapped for the tensor cores: 16 rows of W fill the M side of an
-// mma.sync m16n8k16, 8 tokens fill the N side.  Every thread fetches its
-// fragments with 16-byte loads straight from global memory: the four lanes
-// of a quad read 8 consecutive k each (32 k in all), which is two k16 steps
-// of the instruction under a fixed permutation of k that X is loaded with as
-// well, so no shared memory or ldmatrix is needed on the way in.
+// mma.sync m16n8k16, 8 tokens fill the N side.  Every thread fetches its own
+// fragments in 16-byte pieces: the four lanes of a quad read 8 consecutive k
+// each (32 k in all), which is two k16 steps of the instruction under a fixed
+// permutation of k that X is loaded with as well, so no ldmatrix and no
+// exchange between threads is needed on the way in.
 //
 // A block owns a few 16-row tiles of W over the whole of K; its 8 warps take
-// interleaved 64-wide blocks of K with the next block's loads in flight, and
-// add their partial sums in shared memory in warp order (the result does not
+// interleaved 64-wide blocks of K.  The weights of the next DEPTH blocks of a
+// warp are in flight at any time: cp.async copies each thread's pieces into a
+// slot of shared memory that only this thread reads back (a queue per thread,
+// no barrier), which is what it takes to keep the memory busy at the latency
+// it has.  The warps add their partial sums in shared memory in warp order (the result does not
 // depend on scheduling).  Epilogues: plain store (bfloat16 or float), the
 // gated activation act(gate) * up for W = [Wg; Wu] (wlejon/brolm
 // src/gemma2.cpp:378-381), cap * tanh(y / cap) into float logits
@@ -27,6 +30,10 @@ namespace {
 
 constexpr int WARPS = 8;
 constexpr int KB = 64;     // k per warp iteration
+// Blocks of K whose weights a warp has in flight; the queue has one slot more.  A slot of a block is
+// MT * 16 KB: three blocks of 64 KB (MT 1) or two of 96 KB (MT 2) share an SM, one of 192 KB (MT 4) has it alone.
+template <int MT> __host__ __device__ constexpr int depth() { return MT == 1 ? 3 : 2; }
+template <int MT> __host__ __device__ constexpr size_t queue_bytes() { return (size_t)(depth<MT>() + 1) * WARPS * (4 * MT) * 32 * 16; }
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -35,10 +42,15 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 ldg16(const bf16* p, bool ok) {
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (ok) asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+// 16 bytes from global memory into this thread's slot of the queue (zeros when !ok)
+__device__ __forceinline__ void copy16(uint32_t dst, const bf16* p, bool ok) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(p), "r"(ok ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copy_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
 __device__ __forceinline__ uint4 ldg16_cached(const bf16* p, bool ok) {
@@ -81,7 +93,6 @@ struct SkinnyArgs {
 // MT: 16-row tiles of W per block.  NT: 8-token tiles.
 template <int MT, int NT, int EPI>
 __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
-    __shared__ float red[WARPS][MT * NT * 4][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int q = lane & 3, r = lane >> 2;
     constexpr int OUT_TILES = EPI == EPI_GATED ? MT / 2 : MT;      // 16-column tiles of Y per block
@@ -113,18 +124,26 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
     const int nkb_all = (a.K + KB - 1) / KB;
     const int per = (nkb_all + a.ksplit - 1) / a.ksplit;
     const int kb_first = blockIdx.y * per, nkb = min(nkb_all, kb_first + per);
-    uint4 wc[2][MT][2], xc[2][NT];                                 // [half of the block][tile][row r / r + 8]
+    uint4 xc[2][NT];                                               // [half of the block][token tile]
+    extern __shared__ __align__(16) uint8_t queue_raw[];
+    constexpr int DEPTH = depth<MT>();
+    constexpr int PIECES = 4 * MT;                                 // 16-byte pieces of a thread per block of K
+    const uint32_t queue = (uint32_t)__cvta_generic_to_shared(queue_raw) + (warp * PIECES * 32 + lane) * 16;
+    auto slot_of = [&](int n) { return queue + (uint32_t)(n % (DEPTH + 1)) * (WARPS * PIECES * 32 * 16); };
 
-    auto load_w = [&](int kb, uint4 (&wv)[2][MT][2]) {
+    // asks for the weights of the warp's n-th block of K (block kb); pieces: [half][tile][row r / its partner]
+    auto fetch_w = [&](int kb, int n) {
+        const uint32_t dst = slot_of(n);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int kk = kb * KB + h * 32 + q * 8;
-            const bool kok = kk < a.K;                              // K is a multiple of 8
+            const bool kok = kb < nkb && kk < a.K;                  // K is a multiple of 8
 #pragma unroll
             for (int i = 0; i < MT; ++i) {
                 const int col = (EPI == EPI_GATED ? wrow[i] - ((i & 1) ? a.N : 0) : wrow[i]) + r;   // output column of row r
-                wv[h][i][0] = ldg16(a.w + (size_t)(wrow[i] + r) * a.ldw + kk, kok && col < n_limit);
-                wv[h][i][1] = ldg16(a.w + (size_t)(wrow[i] + r + half) * a.ldw + kk, kok && col + half < n_limit);
+                const bool ok0 = kok && col < n_limit, ok1 = kok && col + half < n_limit;
+                copy16(dst + ((h * MT + i) * 2) * 512, a.w + (ok0 ? (size_t)(wrow[i] + r) * a.ldw + kk : 0), ok0);
+                copy16(dst + ((h * MT + i) * 2 + 1) * 512, a.w + (ok1 ? (size_t)(wrow[i] + r + half) * a.ldw + kk : 0), ok1);
             }
         }
     };
@@ -141,43 +160,55 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
     };
     (void)w_rows;
 
-    // The weights depend on nothing that ran before: their first loads go out while the kernel
-    // before this one is still finishing; X is its output and has to wait.
-    int kb = kb_first + warp;
-    if (kb < nkb) load_w(kb, wc);
+    // The weights depend on nothing that ran before: the first DEPTH blocks are asked for while the
+    // kernel before this one is still finishing; X is its output and has to wait.
+    const int kb0 = kb_first + warp;
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+        fetch_w(kb0 + d * WARPS, d);
+        copy_commit();
+    }
     pdl_wait();
-    if (kb < nkb) load_x(kb, xc);
-    for (; kb < nkb; kb += WARPS) {
-        uint4 wn[2][MT][2], xn[2][NT];
+    if (kb0 < nkb) load_x(kb0, xc);
+    int n = 0;
+    for (int kb = kb0; kb < nkb; kb += WARPS, ++n) {
+        uint4 xn[2][NT];
         const bool more = kb + WARPS < nkb;
-        if (more) { load_w(kb + WARPS, wn); load_x(kb + WARPS, xn); }
+        if (more) load_x(kb + WARPS, xn);
+        // block n + DEPTH goes into the slot that block n - 1 was read from
+        fetch_w(kb + DEPTH * WARPS, n + DEPTH);
+        copy_commit();
+        copy_wait<DEPTH>();                                         // block n has landed
+        const uint32_t src = slot_of(n);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
             for (int i = 0; i < MT; ++i) {
+                const uint4 w0 = lds16(src + ((h * MT + i) * 2) * 512), w1 = lds16(src + ((h * MT + i) * 2 + 1) * 512);
 #pragma unroll
                 for (int j = 0; j < NT; ++j) {
-                    mma_bf16(acc[i][j], wc[h][i][0].x, wc[h][i][1].x, wc[h][i][0].y, wc[h][i][1].y, xc[h][j].x, xc[h][j].y);
-                    mma_bf16(acc[i][j], wc[h][i][0].z, wc[h][i][1].z, wc[h][i][0].w, wc[h][i][1].w, xc[h][j].z, xc[h][j].w);
+                    mma_bf16(acc[i][j], w0.x, w1.x, w0.y, w1.y, xc[h][j].x, xc[h][j].y);
+                    mma_bf16(acc[i][j], w0.z, w1.z, w0.w, w1.w, xc[h][j].z, xc[h][j].w);
                 }
             }
         }
         if (more) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-#pragma unroll
-                for (int i = 0; i < MT; ++i) { wc[h][i][0] = wn[h][i][0]; wc[h][i][1] = wn[h][i][1]; }
+            for (int h = 0; h < 2; ++h)
 #pragma unroll
                 for (int j = 0; j < NT; ++j) xc[h][j] = xn[h][j];
-            }
         }
     }
+    copy_wait<0>();
 
     // The stream of weights is over: the next kernel may take its place on the SMs now.  (Letting it in
     // earlier packs its blocks onto the few SMs that happen to have room, and they then run unevenly.)
     pdl_trigger();
 
-    // partial sums of the warps -> shared memory, then summed in warp order
+    // partial sums of the warps -> shared memory (the queue is drained and free), then summed in warp order
+    static_assert(sizeof(float) * WARPS * MT * NT * 4 * 32 <= queue_bytes<MT>(), "the sums fit where the queue was");
+    float (*red)[MT * NT * 4][32] = reinterpret_cast<float (*)[MT * NT * 4][32]>(queue_raw);
+    __syncthreads();
 #pragma unroll
     for (int i = 0; i < MT; ++i)
 #pragma unroll
@@ -261,7 +292,14 @@ template <int MT, int NT, int EPI>
 int launch(const SkinnyArgs& a, cudaStream_t stream) {
     constexpr int cols = (EPI == EPI_GATED ? MT / 2 : MT) * 16;
     dim3 blocks((a.N + cols - 1) / cols, a.ksplit);        // (EPI_ROPE: hd is a multiple of 16, so N is too)
-    return launch_pdl(skinny_kernel<MT, NT, EPI>, blocks, dim3(WARPS * 32), 0, stream, a);
+    constexpr size_t smem = queue_bytes<MT>();
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(skinny_kernel<MT, NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        raised = true;
+    }
+    return launch_pdl(skinny_kernel<MT, NT, EPI>, blocks, dim3(WARPS * 32), smem, stream, a);
 }
 
 template <int EPI>
