@@ -106,7 +106,13 @@ struct MmaArgs {
     int n_splits;
     float* part_o;          // [B][n_q][n_splits][hd]
     float* part_ml;         // [B][n_q][n_splits][2]  (max in log2 units, sum)
+    int merge_here;         // decoding: the last block of a (sequence, kv head) merges the splits itself
 };
+
+// Tickets of the split-KV decode kernel, one per (sequence, kv head); zero between launches.
+constexpr int MAX_TICKETS = 1 << 16;
+__device__ unsigned g_decode_tickets[MAX_TICKETS];
+constexpr int MAX_MERGED_SPLITS = 64;
 
 // s (raw dot product) -> score in log2 units, soft-capped
 __device__ __forceinline__ float score_of(float s, float scale, float cap, float inv_cap) {
@@ -520,6 +526,50 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
             }
         }
     }
+    if (a.n_splits == 1 || !a.merge_here) return;
+
+    // The block that finishes last among the splits of this (sequence, kv head) merges them:
+    //     out = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m).
+    // Every block publishes its partial results (fence), then takes a ticket; the last ticket sees them all.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned* ticket = &g_decode_tickets[(size_t)b * a.n_kv + g];
+        const unsigned prev = atomicAdd(ticket, 1u);
+        is_last = prev == (unsigned)a.n_splits - 1u;
+        if (is_last) *ticket = 0u;                       // all have arrived: ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    float* factor = reinterpret_cast<float*>(stage0);    // [group][n_splits], then the sums [group]
+    float* total = factor + a.group * a.n_splits;
+    for (int row = warp; row < a.group; row += NTHREADS / 32) {      // a warp per head
+        const size_t slot0 = ((size_t)b * n_q + g * a.group + row) * a.n_splits;
+        float mx = -INFINITY;
+        for (int s = lane; s < a.n_splits; s += 32) mx = fmaxf(mx, __ldcg(a.part_ml + (slot0 + s) * 2));
+        mx = warp_max(mx);
+        float sum = 0.0f;
+        for (int s = lane; s < a.n_splits; s += 32) {
+            const float f = mx > -INFINITY ? fast_exp2(__ldcg(a.part_ml + (slot0 + s) * 2) - mx) : 0.0f;
+            factor[row * a.n_splits + s] = f;
+            sum += __ldcg(a.part_ml + (slot0 + s) * 2 + 1) * f;
+        }
+        sum = warp_sum(sum);
+        if (lane == 0) total[row] = sum;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < a.group * hd; idx += NTHREADS) {
+        const int row = idx / hd, d = idx - row * hd;
+        const size_t slot0 = ((size_t)b * n_q + g * a.group + row) * a.n_splits;
+        float acc = 0.0f;
+#pragma unroll 4
+        for (int s = 0; s < a.n_splits; ++s) acc += __ldcg(a.part_o + (slot0 + s) * hd + d) * factor[row * a.n_splits + s];
+        const float sum = total[row];
+        a.out[(size_t)a.cu_q[b] * a.out_stride + (g * a.group + row) * hd + d] =
+            __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
+    }
 }
 
 // Merge the splits of one (sequence, head): out = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m).
@@ -581,8 +631,11 @@ int launch_decode(const MmaArgs& a, int batch, cudaStream_t stream) {
         allowed = smem;
     }
     dim3 grid(a.n_splits, a.n_kv, batch);
-    int st = launch_pdl(attn_decode_mma_kernel<HD_MAX, EXACT>, grid, dim3(NTHREADS), smem, stream, a);
-    if (st != 0 || a.n_splits == 1) return st;
+    MmaArgs b = a;
+    b.merge_here = a.n_splits > 1 && a.n_splits <= MAX_MERGED_SPLITS && (long long)batch * a.n_kv <= MAX_TICKETS &&
+                   (size_t)(a.group * a.n_splits + a.group) * sizeof(float) <= smem - 16 * a.hd * sizeof(bf16);
+    int st = launch_pdl(attn_decode_mma_kernel<HD_MAX, EXACT>, grid, dim3(NTHREADS), smem, stream, b);
+    if (st != 0 || a.n_splits == 1 || b.merge_here) return st;
     dim3 cgrid(a.n_kv * a.group, batch);
     return launch_pdl(attn_combine_kernel, cgrid, dim3(128), (a.n_splits + 33) * sizeof(float), stream,
                       (const float*)a.part_o, (const float*)a.part_ml, a.out, a.cu_q, a.out_stride,
