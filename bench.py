@@ -149,6 +149,8 @@ def main() -> int:
     def decode_run(batch: int, context: int, steps: int, warmup: int):
         """Decode ``steps`` tokens per sequence after ``warmup`` untimed ones, ending at ``context`` tokens.
 
+        A step reads every weight and the live cache once, gigabytes against an L2 of 126 MB, so
+        nothing of one step is still cached for the next and no flush is put between steps.
         Two passes over the same prompts.  End to end: ``brolm_b200.generate`` with host token ids in and
         out; every step copies the step's tokens from pinned host memory to the device and reads the
         sampled ids back.  Device: the same steps fed with the tokens the first pass produced, queued
@@ -166,7 +168,6 @@ def main() -> int:
         def on_step(produced: int, active: int) -> None:
             # called after the step's tokens reached the host
             stamps.append(time.perf_counter())
-            flush.zero_()                                   # between steps: push the weights out of L2
 
         with ClockSampler() as clocks:
             out = bb.generate(engine, prompts, eos_id=-1, opts=opts, on_step=on_step)
@@ -188,7 +189,6 @@ def main() -> int:
                     ev.record()
                     events.append(ev)
                     launches.append(kernels.launch_count())
-                flush.zero_()
                 logits = engine.step(slots, [[o[i]] for o in out])
                 sampler(logits, streams, i + 1)
             ev = torch.cuda.Event(enable_timing=True)
@@ -197,17 +197,8 @@ def main() -> int:
             launches.append(kernels.launch_count())
             torch.cuda.synchronize()
             engine.close(slots)
-        dev_ms = events[0].elapsed_time(events[-1])
-        # the flush between steps is inside both windows: time it alone and take it out
-        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        f0.record()
-        for _ in range(steps):
-            flush.zero_()
-        f1.record()
-        torch.cuda.synchronize()
-        flush_ms = f0.elapsed_time(f1)
-        ms = (dev_ms - flush_ms) / steps
-        return {"tok_s": batch * 1000.0 / ms, "ms": ms, "e2e_tok_s": batch * steps / (e2e_s - flush_ms / 1000.0),
+        ms = events[0].elapsed_time(events[-1]) / steps
+        return {"tok_s": batch * 1000.0 / ms, "ms": ms, "e2e_tok_s": batch * steps / e2e_s,
                 "launches": launches[-1] - launches[0], "clocks": clocks.summary(),
                 "h2d": engine.last_h2d_bytes, "d2h": 4 * batch}
 
@@ -225,7 +216,8 @@ def main() -> int:
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "sliding_window": cfg.sliding_window, "global_batch": args.batch, "seq_len": args.context,
-                   "parallelism": "none (1 GPU)", "l2": "flushed between steps (256 MB write)",
+                   "parallelism": "none (1 GPU)",
+                   "l2": f"inputs larger than L2 ({bytes_step / 1e9:.1f} GB read per step)",
                    "peaks": pk["source"]},
         "clocks": main_run["clocks"],
         "e2e": {"value": round(main_run["e2e_tok_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": main_run["h2d"],

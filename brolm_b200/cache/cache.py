@@ -127,6 +127,7 @@ class Cache:
         self.dtype, self.device = dtype, torch.device(device)
         self.slots = SlotTable(self.max_slots)
         self.lengths = [0] * self.max_slots
+        self.epochs = [0] * self.max_slots        # how often a slot has been taken: tells one tenant from the next
         self.kv_groups: list[KVGroup] = []
         self.state_groups: list[StateGroup] = []
         self.entries: list[Optional[CacheEntry]] = [None] * len(specs)
@@ -157,6 +158,7 @@ class Cache:
     def alloc_slot(self) -> int:
         slot = self.slots.alloc()
         self.lengths[slot] = 0
+        self.epochs[slot] += 1
         for g in self.kv_groups:
             g.pages[slot] = []
         for g in self.state_groups:
@@ -242,6 +244,25 @@ class Cache:
                 rows[pos < b - g.ring] = -1
             out.append(rows)
         return np.concatenate(out) if out else np.zeros(0, dtype=np.int64)
+
+    def pages_signature(self, group_id: int, slots: Sequence[int]) -> tuple:
+        """Changes whenever the page table of these slots does: pages are only ever appended to a
+        slot's list, and a slot that was given back and taken again has a new epoch."""
+        g = self.kv_groups[group_id]
+        return tuple((s, self.epochs[s], len(g.pages[s])) if s >= 0 else (-1, 0, 0) for s in slots)
+
+    def decode_rows(self, group_id: int, slots: Sequence[int], positions: Sequence[int]) -> list:
+        """``write_rows`` for one new token per slot at ``positions`` (the decode step), without arrays."""
+        g = self.kv_groups[group_id]
+        P, ring = g.page_size, g.ring
+        out = []
+        for s, pos in zip(slots, positions):
+            if s < 0:
+                out.append(-1)
+                continue
+            r = pos % ring if ring else pos
+            out.append(g.pages[s][r // P] * P + r % P)
+        return out
 
     def entry(self, i: int) -> CacheEntry:
         e = self.entries[i]

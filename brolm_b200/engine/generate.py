@@ -84,9 +84,12 @@ def _run_batch(engine, sampler, prompts, batch, slots, max_new, stops, results, 
     active = list(range(len(batch)))                     # indices into batch / slots
     tokens = [list(prompts[r]) for r in batch]
     produced = 0
+    streams, streams_of = None, None
     while active:
         logits = engine.step([slots[a] for a in active], [tokens[a] for a in active])
-        streams = torch.tensor([batch[a] for a in active], dtype=torch.int32).to(device)
+        if streams_of != active:                           # the request numbers change only when a request ends
+            streams = torch.tensor([batch[a] for a in active], dtype=torch.int32).to(device)
+            streams_of = list(active)
         drawn = sampler(logits, streams, produced).tolist()
         produced += 1
         if on_step:

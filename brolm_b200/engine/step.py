@@ -65,6 +65,7 @@ class _DecodeGraph:
         n = 4 * rows + sum(rows * w for w in self.widths) + rows * len(self.widths)
         self.host = torch.zeros(n, dtype=torch.int32, pin_memory=True)
         self.hv = self.host.numpy()
+        self.table_sig = [None] * len(self.widths)      # what the page tables in the pinned buffer were made from
         self.dev = torch.zeros(n, dtype=torch.int32, device=dev)
         seg = [self.dev[i * rows:(i + 1) * rows] for i in range(4)]
         off = 4 * rows
@@ -122,12 +123,22 @@ class _DecodeGraph:
         hv[3 * R:3 * R + B] = plan.slots
         off = 4 * R
         for g, w in enumerate(self.widths):
-            t = cache.page_table(g, plan.slots, width=w, rows=R)
-            hv[off:off + R * w] = t.numpy().reshape(-1)
+            # the page tables change only when a sequence begins a page or the batch changes
+            sig = cache.pages_signature(g, plan.slots)
+            if sig != self.table_sig[g]:
+                view = hv[off:off + R * w].reshape(R, w)
+                view[:] = 0
+                pages = cache.kv_groups[g].pages
+                for r, s in enumerate(plan.slots):
+                    l = pages[s]
+                    if len(l) > w:
+                        raise CacheError("page table width is too small")
+                    view[r, :len(l)] = l
+                self.table_sig[g] = sig
             off += R * w
         hv[off:] = -1
         for g in range(len(self.widths)):
-            hv[off + g * R:off + g * R + B] = cache.write_rows(g, plan.slots, plan.old, plan.new_len)
+            hv[off + g * R:off + g * R + B] = cache.decode_rows(g, plan.slots, plan.old)
         self.dev.copy_(self.host, non_blocking=True)
         self.copied.record()
         self.graph.replay()

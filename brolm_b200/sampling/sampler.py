@@ -30,10 +30,15 @@ def uniform24(seed: int, stream: int, counter: int) -> float:
 class Sampler:
     def __init__(self, params: SamplingParams):
         self.params = params
+        self._out: dict = {}
 
     def __call__(self, logits: torch.Tensor, streams: torch.Tensor, counter: int) -> torch.Tensor:
-        """logits [rows, vocab] float32; streams int32 [rows]; returns int32 [rows] on the device."""
-        out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+        """logits [rows, vocab] float32; streams int32 [rows]; returns int32 [rows] on the device
+        (a buffer of the sampler's, written again by its next call with as many rows)."""
+        key = (logits.shape[0], logits.device)
+        out = self._out.get(key)                 # valid until the next call with as many rows
+        if out is None:
+            out = self._out[key] = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
         p = self.params
         if p.greedy:
             kernels.argmax(logits, out)
