@@ -136,3 +136,43 @@ def test_write_rows_follow_the_pages_and_skip_what_the_ring_drops():
     c.reserve({a: 301, b: 4})
     rows = c.write_rows(1, [a, -1, b], [300, 0, 3], [301, 1, 4])       # a decode step with a padding row
     assert rows.tolist() == [win.pages[a][(300 % 128) // 64] * 64 + 300 % 64, -1, win.pages[b][0] * 64 + 3]
+
+
+def test_decode_rows_equal_write_rows_for_one_token():
+    """The decode step's scalar form of write_rows: the same places, through the ring's wrap as well."""
+    cache = Cache([KVSpec(2, 16, None), KVSpec(2, 16, 96)], max_tokens=64 * 12, dtype=torch.float32, device="cpu",
+                  max_slots=3)
+    slots = [cache.alloc_slot() for _ in range(3)]
+    lengths = [0, 0, 0]
+    rng = random.Random(3)
+    first = [5, 70, 130]
+    cache.reserve(dict(zip(slots, first)))
+    cache.commit(dict(zip(slots, first)))
+    lengths = list(first)
+    for _ in range(150):
+        new = [n + 1 for n in lengths]
+        cache.reserve(dict(zip(slots, new)))
+        for g in range(2):
+            want = cache.write_rows(g, slots + [-1], lengths + [0], new + [1]).tolist()
+            assert cache.decode_rows(g, slots + [-1], lengths + [0]) == want
+        cache.commit(dict(zip(slots, new)))
+        lengths = new
+
+
+def test_pages_signature_changes_with_the_table():
+    cache = Cache([KVSpec(1, 16, None)], max_tokens=64 * 8, dtype=torch.float32, device="cpu", max_slots=2)
+    a = cache.alloc_slot()
+    cache.reserve({a: 10})
+    cache.commit({a: 10})
+    sig = cache.pages_signature(0, [a, -1])
+    cache.reserve({a: 64})
+    assert cache.pages_signature(0, [a, -1]) == sig            # same page
+    cache.reserve({a: 65})
+    assert cache.pages_signature(0, [a, -1]) != sig            # a page was added
+    sig = cache.pages_signature(0, [a])
+    pages = list(cache.kv_groups[0].pages[a])
+    cache.free_slot(a)
+    b = cache.alloc_slot()
+    cache.reserve({b: 65})
+    assert b == a and len(cache.kv_groups[0].pages[b]) == len(pages)
+    assert cache.pages_signature(0, [b]) != sig                # the same slot, another tenant
