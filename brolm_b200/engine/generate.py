@@ -70,10 +70,14 @@ def generate(engine, prompts: Sequence[Sequence[int]], eos_id: int = -1,
     cache = engine.cache
     batches = plan_batches([len(p) for p in prompts], opts.max_new_tokens, cache.max_tokens, cache.max_slots,
                            cache.page_size, batch_size)
+    device = getattr(engine, "device", None)
+    ahead = (hasattr(engine, "step_from") and isinstance(device, torch.device) and device.type == "cuda"
+             and isinstance(sampler, Sampler))
+    run = _run_batch_ahead if ahead else _run_batch
     for batch in batches:
         slots = engine.open(len(batch))
         try:
-            _run_batch(engine, sampler, prompts, batch, slots, opts.max_new_tokens, stops, results, on_step)
+            run(engine, sampler, prompts, batch, slots, opts.max_new_tokens, stops, results, on_step)
         finally:
             engine.close(slots)
     return results
@@ -103,3 +107,55 @@ def _run_batch(engine, sampler, prompts, batch, slots, max_new, stops, results, 
                 tokens[a] = [int(tok)]
                 still.append(a)
         active = still
+
+
+def _run_batch_ahead(engine, sampler, prompts, batch, slots, max_new, stops, results, on_step) -> None:
+    """``_run_batch`` for an engine on a GPU, one step ahead of the host.
+
+    The ids a step draws stay on the device and feed the next step directly (``Engine.step_from``), so
+    that step is queued before the host has read them; the host reads them on a second stream while
+    the GPU is already busy, and learns one step late that a sequence has drawn a stop token.  The
+    step that was queued for that sequence in the meantime is wasted (its row is sampled and thrown
+    away, its slot goes back with the batch); what is returned, the random numbers of the draws and
+    the budget are those of ``_run_batch``.
+    """
+    device = engine.device
+    n = len(batch)
+    side = torch.cuda.Stream(device=device)
+    drawn_host = torch.empty(n, dtype=torch.int32, pin_memory=True)
+    drawn_ready, ids_ready = torch.cuda.Event(), torch.cuda.Event()
+    stopped = [False] * n
+    queued = [0] * n                                   # tokens drawn or being drawn for each request
+    rows = list(range(n))                              # the requests whose logits the last step left, in row order
+    logits = engine.step([slots[a] for a in rows], [list(prompts[batch[a]]) for a in rows])
+    streams, streams_of = None, None
+    produced = 0
+    while rows:
+        if streams_of != rows:
+            streams = torch.tensor([batch[a] for a in rows], dtype=torch.int32).to(device)
+            streams_of = list(rows)
+        ids = sampler(logits, streams, produced)
+        produced += 1
+        for a in rows:
+            queued[a] += 1
+        # the host's copy of the ids, on a stream of its own: the next step does not wait for it
+        ids_ready.record()
+        side.wait_event(ids_ready)
+        with torch.cuda.stream(side):
+            drawn_host[:len(rows)].copy_(ids, non_blocking=True)
+            drawn_ready.record()
+        ahead = [a for a in rows if not stopped[a] and queued[a] < max_new]
+        if ahead:
+            logits = engine.step_from([slots[a] for a in ahead], ids, [rows.index(a) for a in ahead])
+        drawn_ready.synchronize()
+        drawn = drawn_host[:len(rows)].tolist()
+        if on_step:
+            on_step(produced, len(rows))
+        for a, tok in zip(rows, drawn):
+            if stopped[a]:
+                continue                                  # drawn for a sequence that had already ended
+            if tok in stops:
+                stopped[a] = True                         # the stop token is not returned
+            else:
+                results[batch[a]].append(int(tok))
+        rows = ahead

@@ -63,6 +63,8 @@ class _DecodeGraph:
                 w = min(w, g.ring // g.page_size)
             self.widths.append(max(1, w))
         n = 4 * rows + sum(rows * w for w in self.widths) + rows * len(self.widths)
+        self.pick_off = n                    # last: which element of a tensor of drawn ids each row's token is
+        n += rows
         self.host = torch.zeros(n, dtype=torch.int32, pin_memory=True)
         self.hv = self.host.numpy()
         self.table_sig = [None] * len(self.widths)      # what the page tables in the pinned buffer were made from
@@ -76,6 +78,7 @@ class _DecodeGraph:
         self.rows_off = off
         cache_rows = [self.dev[off + g * rows:off + (g + 1) * rows] for g in range(len(self.widths))]
         self.tokens = seg[0]
+        self.pick = self.dev[self.pick_off:self.pick_off + rows]
         ar = torch.arange(rows + 1, dtype=torch.int32, device=dev)
         self.ctx = StepContext(
             mode="decode", dtype=engine.model.dtype, device=dev, cache=cache, batch=rows, n_tokens=rows, slots=[],
@@ -85,7 +88,7 @@ class _DecodeGraph:
         # an all-padding state: the warm-up pass touches no cache
         self.hv[:] = 0
         self.hv[rows:2 * rows] = -1
-        self.hv[self.rows_off:] = -1
+        self.hv[self.rows_off:self.pick_off] = -1
         self.dev.copy_(self.host)
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
@@ -111,7 +114,10 @@ class _DecodeGraph:
                 gc.enable()
         self.kernels = kernels.launch_count() - before      # this library's kernels in one replay
 
-    def run(self, plan: _Plan, cache: Cache) -> torch.Tensor:
+    def run(self, plan: _Plan, cache: Cache, ids: Optional[torch.Tensor] = None,
+            pick: Optional[Sequence[int]] = None) -> torch.Tensor:
+        """``ids``/``pick``: the tokens are not the plan's but ``ids[pick[i]]``, ids an int32 tensor on the
+        device (what a sampler has just drawn): they are gathered on the device, in stream order."""
         R, B = self.rows, len(plan.slots)
         hv = self.hv
         self.copied.synchronize()              # the copy of the step before has left the pinned buffer
@@ -136,11 +142,15 @@ class _DecodeGraph:
                     view[r, :len(l)] = l
                 self.table_sig[g] = sig
             off += R * w
-        hv[off:] = -1
+        hv[off:self.pick_off] = -1
         for g in range(len(self.widths)):
             hv[off + g * R:off + g * R + B] = cache.decode_rows(g, plan.slots, plan.old)
+        if ids is not None:
+            hv[self.pick_off:self.pick_off + B] = pick
         self.dev.copy_(self.host, non_blocking=True)
         self.copied.record()
+        if ids is not None:
+            torch.index_select(ids, 0, self.pick[:B], out=self.tokens[:B])
         self.graph.replay()
         kernels.add_launches(self.kernels)
         return self.logits
@@ -206,6 +216,29 @@ class Engine:
                 if code:
                     raise StepError(f"step: a wait inside a tensor-core kernel ran out (code {code}); "
                                     f"the results of this step are not valid")
+        self.cache.commit(dict(zip(plan.slots, plan.new_len)))
+        return logits
+
+    def step_from(self, slots: Sequence[int], ids: torch.Tensor, pick: Sequence[int]) -> torch.Tensor:
+        """A decode step whose tokens are still on the device: sequence ``slots[i]`` goes on with
+        ``ids[pick[i]]``, ``ids`` being an int32 tensor that a sampler wrote.  Nothing waits for the
+        values, so the step can be queued before the host has seen them; the logits are those of
+        ``step`` with the same tokens."""
+        if ids.dtype != torch.int32 or ids.dim() != 1 or ids.device != self.device:
+            raise StepError("step_from: ids must be a one-dimensional int32 tensor on the engine's device")
+        if len(pick) != len(slots) or any(not 0 <= int(p) < ids.numel() for p in pick):
+            raise StepError("step_from: one place in ids per slot")
+        plan = self._plan(slots, [[0]] * len(slots), None)
+        if plan.mode != "decode":
+            raise StepError("step_from: only sequences that already hold tokens can go on")
+        if self.use_graphs:
+            graph = self._graph_for(plan)
+            logits = graph.run(plan, self.cache, ids, [int(p) for p in pick])[:len(plan.slots)]
+            self.last_h2d_bytes = graph.host.numel() * 4
+        else:
+            ctx, _, rows = self._context(plan)
+            tokens = ids.index_select(0, torch.tensor([int(p) for p in pick], dtype=torch.int32, device=self.device))
+            logits = self.model.forward(ctx, tokens, rows)
         self.cache.commit(dict(zip(plan.slots, plan.new_len)))
         return logits
 

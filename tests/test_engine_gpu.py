@@ -237,3 +237,36 @@ def test_tensors_stored_in_32_bits_stay_so_and_still_compute(tmp_path):
     for i in range(80, 90):
         check(eng.step([s], [[p[i]]])[0], ref[i], "bfloat16", f"token {i}")
     eng.close([s])
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_generation_one_step_ahead_equals_step_by_step(setups, graphs, temperature):
+    """On a GPU the loop queues the next step from the ids on the device before the host has read them.
+    With stop tokens that do occur, a budget that cuts requests off and more requests than slots, it
+    returns what the step-by-step loop returns (float32: the same ids)."""
+    _, config, weights, model = setups[("B", "float32")]
+    V = config["vocab_size"]
+    prompts = random_prompts(V, [5, 30, 17, 1, 70, 9, 2], seed=61)
+    params = bb.SamplingParams(temperature=temperature, top_k=50 if temperature else 0, seed=7)
+
+    def run(step_by_step, stop_ids, max_new):
+        eng = bb.Engine(model, max_tokens=64 * 8, max_slots=3, use_graphs=graphs)
+        opts = bb.GenerateOptions(max_new_tokens=max_new, sampling=params, stop_on_eos=True, stop_ids=stop_ids)
+        sampler = bb.Sampler(params)
+        if step_by_step:
+            inner = sampler
+            sampler = lambda logits, streams, counter: inner(logits, streams, counter)   # not a Sampler: no run-ahead
+        out = bb.generate(eng, prompts, eos_id=-1, opts=opts, sampler=sampler)
+        assert eng.cache.live_slots == 0
+        return out
+
+    free = run(True, [], 12)
+    # stop ids taken from what is generated: some requests end early, at different steps
+    stop_ids = sorted({o[3] for o in free[:3]} | {free[4][0]})
+    for max_new in (1, 2, 12):
+        a, b = run(True, stop_ids, max_new), run(False, stop_ids, max_new)
+        assert a == b
+        assert any(len(o) < max_new for o in a) or max_new == 1
+        for o in a:
+            assert not set(o) & set(stop_ids) and len(o) <= max_new
