@@ -83,6 +83,13 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+# Decode steps that every run puts between its prompt and its warm-up steps.  The prompt (batch x
+# context tokens at full compute power) leaves the GPU with lowered clocks for some tens of
+# milliseconds: the first 10-30 decode steps after it take up to 1.4 times as long as the steady
+# ones that the metric is about (measured: 3.4, then 2.8, then 2.45 ms at batch 8, context 8192).
+SETTLE = 32
+
+
 def decode_bytes(cfg, layers: int, batch: int, context: int, itemsize: int = 2) -> float:
     """Bytes a decode step has to read: every weight once and the cache of the live requests."""
     H, F = cfg.hidden_size, cfg.intermediate_size
@@ -155,6 +162,7 @@ def main() -> int:
         out; every step copies the step's tokens from pinned host memory to the device and reads the
         sampled ids back.  Device: the same steps fed with the tokens the first pass produced, queued
         without reading anything back, timed with CUDA events."""
+        warmup += SETTLE
         total = steps + warmup
         prompt_len = context - total - 1
         engine = bb.Engine(model, max_tokens=batch * ((context + 63) // 64 * 64), max_slots=batch,
@@ -216,7 +224,7 @@ def main() -> int:
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "sliding_window": cfg.sliding_window, "global_batch": args.batch, "seq_len": args.context,
-                   "parallelism": "none (1 GPU)",
+                   "parallelism": "none (1 GPU)", "settle_steps": SETTLE,
                    "l2": f"inputs larger than L2 ({bytes_step / 1e9:.1f} GB read per step)",
                    "peaks": pk["source"]},
         "clocks": main_run["clocks"],
