@@ -12,7 +12,7 @@ from typing import Optional
 
 import torch
 
-from .build import KernelBuildError, build_all, load_library
+from .build import KernelBuildError, build_all, library_loaded, load_library
 
 F32, BF16 = 0, 1
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
@@ -309,6 +309,8 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: 
 
 def gemm_tc_status(reset: bool = False) -> int:
     """0 if no bounded wait inside gemm_tc ever ran out; otherwise the code of the first one.  Synchronises."""
+    if not library_loaded("gemm_tc"):
+        return 0                   # none of its kernels ever ran: nothing is built or loaded for the question
     f = load_library("gemm_tc").brolm_gemm_tc_status
     f.argtypes = [c_int]
     f.restype = c_int
@@ -363,6 +365,8 @@ def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilog
 
 def gemm_stream_status(reset: bool = False) -> int:
     """0 if no bounded wait inside gemm_stream ever ran out; otherwise its code.  Synchronises."""
+    if not library_loaded("gemm_stream"):
+        return 0                   # none of its kernels ever ran: nothing is built or loaded for the question
     f = load_library("gemm_stream").brolm_gemm_stream_status
     f.argtypes = [c_int]
     f.restype = c_int
@@ -407,8 +411,6 @@ def decode_chain(maps: torch.Tensor, ops: torch.Tensor, first: int, count: int, 
     assert maps.dtype == torch.uint8 and maps.is_contiguous() and sync.dtype == torch.int32 and sync.numel() >= 4
     assert positions.dtype == torch.int32 and positions.numel() >= tokens and len(cache_rows) <= 4
     rows = [_ptr(r) for r in cache_rows] + [None] * (4 - len(cache_rows))
-    global _chain_used
-    _chain_used = True
     f = _fn("decode_chain", "brolm_decode_chain", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     if trace is not None:
@@ -417,13 +419,10 @@ def decode_chain(maps: torch.Tensor, ops: torch.Tensor, first: int, count: int, 
              _ptr(sync), _ptr(trace), _stream()), "decode_chain")
 
 
-_chain_used = False
-
-
 def decode_chain_status(reset: bool = False) -> int:
     """0 if no bounded wait inside the decode chain ever ran out (or none ever ran); otherwise its code.
     Synchronises."""
-    if not _chain_used:
+    if not library_loaded("decode_chain"):
         return 0
     f = load_library("decode_chain").brolm_decode_chain_status
     f.argtypes = [c_int]
@@ -493,6 +492,8 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor,
 
 def attention_tc_status(reset: bool = False) -> int:
     """0 if no bounded wait inside the tcgen05 attention ever ran out; otherwise its code.  Synchronises."""
+    if not library_loaded("attn_tc"):
+        return 0                   # none of its kernels ever ran: nothing is built or loaded for the question
     f = load_library("attn_tc").brolm_attn_tc_status
     f.argtypes = [c_int]
     f.restype = c_int

@@ -173,6 +173,11 @@ def _prune(keep: list[str]) -> None:
                 pass
 
 
+def library_loaded(name: str) -> bool:
+    """Whether this process has already loaded (and so used) the library."""
+    return name in _loaded
+
+
 def load_library(name: str) -> ctypes.CDLL:
     """Build if needed, then load; fails loudly, there is no fallback."""
     with _lock:
