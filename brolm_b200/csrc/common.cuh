@@ -64,6 +64,21 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return scratch[32];
 }
 
+// The same sum with one barrier: every thread adds the warps' sums itself, in warp order.  `scratch`
+// holds 2 x 32 floats and `turn` alternates (0, 1, 0, ...) between consecutive calls of a kernel, so a
+// call never writes what a slower thread may still be reading from the call before.
+__device__ __forceinline__ float block_sum_once(float v, float* scratch, int turn) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    float* mine = scratch + 32 * (turn & 1);
+    if (lane == 0) mine[warp] = v;
+    __syncthreads();
+    float t = 0.0f;
+    for (int w = 0; w < nwarps; ++w) t += mine[w];
+    return t;
+}
+
 __device__ __forceinline__ float block_max(float v, float* scratch) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nwarps = (blockDim.x + 31) >> 5;

@@ -70,7 +70,7 @@ template <typename X, typename W, typename O, int MAXC>
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const X* __restrict__ x, const int32_t* __restrict__ rows,
                                                       const W* __restrict__ w, float eps, float offset,
                                                       O* __restrict__ out, int hidden) {
-    __shared__ float scratch[33];
+    __shared__ float scratch[64];
     const int r = blockIdx.x;
     pdl_trigger();
     pdl_wait();
@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const X* __restrict__ x, c
     float ss = 0.0f;
 #pragma unroll
     for (int c = 0; c < C; ++c) ss += v[c][0] * v[c][0] + v[c][1] * v[c][1] + v[c][2] * v[c][2] + v[c][3] * v[c][3];
-    ss = block_sum(ss, scratch);
+    ss = block_sum_once(ss, scratch, 0);
     const float inv = rsqrtf(ss / (float)hidden + eps);
 #pragma unroll
     for (int c = 0; c < C; ++c) {
@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
                                                                float off_post, const W* __restrict__ w_next,
                                                                float eps_next, float off_next, O* __restrict__ out,
                                                                int hidden) {
-    __shared__ float scratch[33];
+    __shared__ float scratch[64];
     const int r = blockIdx.x;
     float* hr = h + (size_t)r * hidden;
     const Y* yr = y + (size_t)r * hidden;
@@ -231,21 +231,28 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
 #pragma unroll
         for (int e = 0; e < 4; ++e) v[c][e] = res[c][e] = 0.0f;
         if (i < hidden) {
-            load4(yr + i, v[c]);
-            for (int s = 1; s < n_parts; ++s) {
-                float t[4];
-                load4(yr + (size_t)s * part_stride + i, t);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) v[c][e] += t[e];
-            }
+            // every slice's load goes out before the first is added: one round trip to the L2, not one per slice
+            constexpr int AT_ONCE = 4;
             load4(hr + i, res[c]);
+            for (int s0 = 0; s0 < n_parts; s0 += AT_ONCE) {
+                float t[AT_ONCE][4];
+#pragma unroll
+                for (int s = 0; s < AT_ONCE; ++s)
+                    if (s0 + s < n_parts) load4(yr + (size_t)(s0 + s) * part_stride + i, t[s]);
+#pragma unroll
+                for (int s = 0; s < AT_ONCE; ++s)
+                    if (s0 + s < n_parts) {                  // added in the order of the slices
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) v[c][e] += t[s][e];
+                    }
+            }
         }
     }
     if (w_post) {
         float ss = 0.0f;
 #pragma unroll
         for (int c = 0; c < C; ++c) ss += v[c][0] * v[c][0] + v[c][1] * v[c][1] + v[c][2] * v[c][2] + v[c][3] * v[c][3];
-        ss = block_sum(ss, scratch);
+        ss = block_sum_once(ss, scratch, 0);
         const float inv_post = rsqrtf(ss / (float)hidden + eps_post);
 #pragma unroll
         for (int c = 0; c < C; ++c)
@@ -264,7 +271,7 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
         if (i < hidden) store4(hr + i, res[c]);
     }
     if (!w_next) return;
-    ss2 = block_sum(ss2, scratch);
+    ss2 = block_sum_once(ss2, scratch, 1);
     const float inv_next = rsqrtf(ss2 / (float)hidden + eps_next);
 #pragma unroll
     for (int c = 0; c < C; ++c) {
