@@ -560,15 +560,32 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
         if (lane == 0) total[row] = sum;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < a.group * hd; idx += NTHREADS) {
-        const int row = idx / hd, d = idx - row * hd;
+    // four outputs per thread and step, the splits' loads of a step issued together (a step is one
+    // round trip to the L2; with 128 threads, a group of 2 and 256 wide heads there is one step)
+    const int q4 = hd >> 2;
+    for (int idx = threadIdx.x; idx < a.group * q4; idx += NTHREADS) {
+        const int row = idx / q4, d = (idx - row * q4) * 4;
         const size_t slot0 = ((size_t)b * n_q + g * a.group + row) * a.n_splits;
-        float acc = 0.0f;
-#pragma unroll 4
-        for (int s = 0; s < a.n_splits; ++s) acc += __ldcg(a.part_o + (slot0 + s) * hd + d) * factor[row * a.n_splits + s];
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int s0 = 0; s0 < a.n_splits; s0 += 4) {
+            float4 v[4];
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+                if (s0 + s < a.n_splits) v[s] = __ldcg(reinterpret_cast<const float4*>(a.part_o + (slot0 + s0 + s) * hd + d));
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+                if (s0 + s < a.n_splits) {
+                    const float f = factor[row * a.n_splits + s0 + s];
+                    acc.x += v[s].x * f; acc.y += v[s].y * f; acc.z += v[s].z * f; acc.w += v[s].w * f;
+                }
+        }
         const float sum = total[row];
-        a.out[(size_t)a.cu_q[b] * a.out_stride + (g * a.group + row) * hd + d] =
-            __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
+        const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+        bf16* dst = a.out + (size_t)a.cu_q[b] * a.out_stride + (g * a.group + row) * hd + d;
+        dst[0] = __float2bfloat16_rn(acc.x * inv);
+        dst[1] = __float2bfloat16_rn(acc.y * inv);
+        dst[2] = __float2bfloat16_rn(acc.z * inv);
+        dst[3] = __float2bfloat16_rn(acc.w * inv);
     }
 }
 

@@ -160,6 +160,30 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
     };
     (void)w_rows;
 
+    // EPI_ROPE: what this thread's (pair, token) of the epilogue needs from memory — the token's position and
+    // place in the cache (written by the host for this step, not by the kernel before) and the pair's
+    // (cos, sin) — is fetched now, so that the epilogue waits for nothing.
+    constexpr int ROPE_PAIRS = MT * NT * 2 * 32;
+    static_assert(EPI != EPI_ROPE || ROPE_PAIRS <= WARPS * 32, "one (pair, token) per thread");
+    int rope_pos = -1, rope_crow = -1;
+    float2 rope_cs = make_float2(1.0f, 0.0f);
+    if constexpr (EPI == EPI_ROPE) {
+        if ((int)threadIdx.x < ROPE_PAIRS) {
+            const int idx = threadIdx.x;
+            const int ln = idx & 31, e = (idx >> 5) & 1, j = (idx >> 6) % NT, i = (idx >> 6) / NT;
+            const int tok = j * 8 + (ln & 3) * 2 + e, col = wrow[i] + (ln >> 2);
+            if (tok < a.M && col < n_limit) {
+                rope_pos = a.positions[tok];
+                if (rope_pos >= 0) {
+                    const int head = col / a.hd, within = col - head * a.hd;
+                    const bool is_v = head >= a.n_q + a.n_kv;
+                    if (!is_v && a.cos_sin) rope_cs = a.cos_sin[(size_t)rope_pos * half + within];
+                    if (head >= a.n_q && a.k_pages) rope_crow = a.cache_rows[tok];
+                }
+            }
+        }
+    }
+
     // The weights depend on nothing that ran before: the first DEPTH blocks are asked for while the
     // kernel before this one is still finishing; X is its output and has to wait.
     const int kb0 = kb_first + warp;
@@ -218,15 +242,12 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
     __syncthreads();
 
     if (EPI == EPI_ROPE) {
-        // one (pair, token) per thread and step: e & 1 picks the token, rows r and r + 8 are the pair
-        constexpr int PAIRS = MT * NT * 2 * 32;
-        for (int idx = threadIdx.x; idx < PAIRS; idx += WARPS * 32) {
+        // one (pair, token) per thread: e & 1 picks the token, rows r and r + 8 are the pair
+        if ((int)threadIdx.x < ROPE_PAIRS && rope_pos >= 0) {
+            const int idx = threadIdx.x;
             const int ln = idx & 31, e = (idx >> 5) & 1, j = (idx >> 6) % NT, i = (idx >> 6) / NT;
             const int tok = j * 8 + (ln & 3) * 2 + e;
             const int col = wrow[i] + (ln >> 2);                    // first element of the pair in the q/k/v row
-            if (tok >= a.M || col >= n_limit) continue;
-            const int pos = a.positions[tok];
-            if (pos < 0) continue;
             float va = 0.0f, vb = 0.0f;
 #pragma unroll
             for (int w = 0; w < WARPS; ++w) {
@@ -236,8 +257,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
             const int head = col / a.hd, within = col - head * a.hd;
             const bool is_v = head >= a.n_q + a.n_kv, is_k = !is_v && head >= a.n_q;
             if (!is_v && a.cos_sin) {
-                const float2 c = a.cos_sin[(size_t)pos * half + within];
-                const float ra = va * c.x - vb * c.y, rb = va * c.y + vb * c.x;
+                const float ra = va * rope_cs.x - vb * rope_cs.y, rb = va * rope_cs.y + vb * rope_cs.x;
                 va = ra;
                 vb = rb;
             }
@@ -245,16 +265,13 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
             bf16* y = reinterpret_cast<bf16*>(a.y) + (size_t)tok * a.ldy + col;
             y[0] = qa;
             y[half] = qb;
-            if ((is_k || is_v) && a.k_pages) {
-                const int crow = a.cache_rows[tok];
-                if (crow >= 0) {
-                    const int kvh = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
-                    bf16* dst = (is_k ? a.k_pages : a.v_pages) +
-                                (((size_t)(crow / a.page_size) * a.n_kv + kvh) * a.page_size + crow % a.page_size) * a.hd +
-                                within;
-                    dst[0] = qa;
-                    dst[half] = qb;
-                }
+            if (rope_crow >= 0) {
+                const int kvh = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
+                bf16* dst = (is_k ? a.k_pages : a.v_pages) +
+                            (((size_t)(rope_crow / a.page_size) * a.n_kv + kvh) * a.page_size + rope_crow % a.page_size) * a.hd +
+                            within;
+                dst[0] = qa;
+                dst[half] = qb;
             }
         }
         return;
