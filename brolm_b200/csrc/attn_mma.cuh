@@ -322,6 +322,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
 // decoding over the paged cache
 // ===========================================================================
 constexpr int STAGES = 3;
+constexpr int PT_ROW = 512;          // entries of a page-table row kept in shared memory (32768 keys)
 
 template <int HD_MAX, bool EXACT>
 __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
@@ -336,8 +337,15 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
 
     const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    pdl_wait();               // q and the newest key and value come from the kernels before this one
+    // The sequence's length and its row of the page table were written by the host before the step's
+    // first kernel: they are fetched together, ahead of the wait, so that the first tile's address
+    // does not take two more round trips to the L2 after it.
+    __shared__ int pt_row[PT_ROW];
+    for (int i = threadIdx.x; i < min(a.pt_stride, PT_ROW); i += NTHREADS) pt_row[i] = a.page_table[(size_t)b * a.pt_stride + i];
     const int kv_len = a.kv_len[b];
+    const int q_row = a.cu_q[b];                              // (also the host's)
+    __syncthreads();
+    pdl_wait();               // q and the newest key and value come from the kernels before this one
     const int n_q = a.n_kv * a.group;
     const int window = a.window > 0 ? a.window : 0x3fffffff;
     const int pos = kv_len - 1;
@@ -356,11 +364,12 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
         const int r = idx / cpr, c = idx - r * cpr;
         const bool ok = r < a.group && kv_len > 0;
         cp_async16(qs_base + tile_off(r, c, hd, swz),
-                   a.q + (size_t)a.cu_q[b] * a.q_stride + (g * a.group + (ok ? r : 0)) * hd + c * 8, ok ? 16 : 0);
+                   a.q + (size_t)q_row * a.q_stride + (g * a.group + (ok ? r : 0)) * hd + c * 8, ok ? 16 : 0);
     }
     auto page_of = [&](int i) -> int {                        // page that holds the i-th tile of the split
         const int ridx = (int)(((long long)(t_begin + i) * KT) % a.ring);
-        return a.page_table[(size_t)b * a.pt_stride + ridx / KT];
+        const int entry = ridx / KT;
+        return entry < PT_ROW ? pt_row[entry] : a.page_table[(size_t)b * a.pt_stride + entry];
     };
     auto load_tile = [&](int i, int page) {                   // i-th tile of the split into stage i % STAGES
         const int t = t_begin + i;
@@ -516,7 +525,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
         }
         const int head = g * a.group + row;
         if (a.n_splits == 1) {
-            a.out[(size_t)a.cu_q[b] * a.out_stride + head * hd + d] = __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
+            a.out[(size_t)q_row * a.out_stride + head * hd + d] = __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
         } else {
             const size_t slot = ((size_t)b * n_q + head) * a.n_splits + split;
             a.part_o[slot * hd + d] = acc;
@@ -543,18 +552,62 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    if (a.n_splits <= 4) {
+        // up to four splits: a thread fetches the statistics of its row's splits and its four outputs of
+        // every split at once and merges them by itself: one round trip to the L2, no exchange
+        const int q4 = hd >> 2;
+        for (int idx = threadIdx.x; idx < a.group * q4; idx += NTHREADS) {
+            const int row = idx / q4, d = (idx - row * q4) * 4;
+            const size_t slot0 = ((size_t)b * n_q + g * a.group + row) * a.n_splits;
+            float4 v[4];
+            float2 ml[4];
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+                if (s < a.n_splits) {
+                    ml[s] = __ldcg(reinterpret_cast<const float2*>(a.part_ml + (slot0 + s) * 2));
+                    v[s] = __ldcg(reinterpret_cast<const float4*>(a.part_o + (slot0 + s) * hd + d));
+                }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+                if (s < a.n_splits) mx = fmaxf(mx, ml[s].x);
+            float sum = 0.0f;
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+                if (s < a.n_splits) {
+                    const float f = mx > -INFINITY ? fast_exp2(ml[s].x - mx) : 0.0f;
+                    sum += ml[s].y * f;
+                    acc.x += v[s].x * f; acc.y += v[s].y * f; acc.z += v[s].z * f; acc.w += v[s].w * f;
+                }
+            const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+            bf16* dst = a.out + (size_t)q_row * a.out_stride + (g * a.group + row) * hd + d;
+            dst[0] = __float2bfloat16_rn(acc.x * inv);
+            dst[1] = __float2bfloat16_rn(acc.y * inv);
+            dst[2] = __float2bfloat16_rn(acc.z * inv);
+            dst[3] = __float2bfloat16_rn(acc.w * inv);
+        }
+        return;
+    }
     float* factor = reinterpret_cast<float*>(stage0);    // [group][n_splits], then the sums [group]
     float* total = factor + a.group * a.n_splits;
     for (int row = warp; row < a.group; row += NTHREADS / 32) {      // a warp per head
         const size_t slot0 = ((size_t)b * n_q + g * a.group + row) * a.n_splits;
-        float mx = -INFINITY;
-        for (int s = lane; s < a.n_splits; s += 32) mx = fmaxf(mx, __ldcg(a.part_ml + (slot0 + s) * 2));
-        mx = warp_max(mx);
+        // (maximum, sum) of up to 64 splits live in the lanes' registers: one fetch for both passes
+        float2 ml0 = make_float2(-INFINITY, 0.0f), ml1 = ml0;
+        if (lane < a.n_splits) ml0 = __ldcg(reinterpret_cast<const float2*>(a.part_ml + (slot0 + lane) * 2));
+        if (lane + 32 < a.n_splits) ml1 = __ldcg(reinterpret_cast<const float2*>(a.part_ml + (slot0 + lane + 32) * 2));
+        const float mx = warp_max(fmaxf(ml0.x, ml1.x));
         float sum = 0.0f;
-        for (int s = lane; s < a.n_splits; s += 32) {
-            const float f = mx > -INFINITY ? fast_exp2(__ldcg(a.part_ml + (slot0 + s) * 2) - mx) : 0.0f;
-            factor[row * a.n_splits + s] = f;
-            sum += __ldcg(a.part_ml + (slot0 + s) * 2 + 1) * f;
+        if (lane < a.n_splits) {
+            const float f = mx > -INFINITY ? fast_exp2(ml0.x - mx) : 0.0f;
+            factor[row * a.n_splits + lane] = f;
+            sum += ml0.y * f;
+        }
+        if (lane + 32 < a.n_splits) {
+            const float f = mx > -INFINITY ? fast_exp2(ml1.x - mx) : 0.0f;
+            factor[row * a.n_splits + lane + 32] = f;
+            sum += ml1.y * f;
         }
         sum = warp_sum(sum);
         if (lane == 0) total[row] = sum;
@@ -567,13 +620,13 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
         const int row = idx / q4, d = (idx - row * q4) * 4;
         const size_t slot0 = ((size_t)b * n_q + g * a.group + row) * a.n_splits;
         float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (int s0 = 0; s0 < a.n_splits; s0 += 4) {
-            float4 v[4];
+        for (int s0 = 0; s0 < a.n_splits; s0 += 8) {
+            float4 v[8];
 #pragma unroll
-            for (int s = 0; s < 4; ++s)
+            for (int s = 0; s < 8; ++s)
                 if (s0 + s < a.n_splits) v[s] = __ldcg(reinterpret_cast<const float4*>(a.part_o + (slot0 + s0 + s) * hd + d));
 #pragma unroll
-            for (int s = 0; s < 4; ++s)
+            for (int s = 0; s < 8; ++s)
                 if (s0 + s < a.n_splits) {
                     const float f = factor[row * a.n_splits + s0 + s];
                     acc.x += v[s].x * f; acc.y += v[s].y * f; acc.z += v[s].z * f; acc.w += v[s].w * f;
@@ -581,7 +634,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
         }
         const float sum = total[row];
         const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
-        bf16* dst = a.out + (size_t)a.cu_q[b] * a.out_stride + (g * a.group + row) * hd + d;
+        bf16* dst = a.out + (size_t)q_row * a.out_stride + (g * a.group + row) * hd + d;
         dst[0] = __float2bfloat16_rn(acc.x * inv);
         dst[1] = __float2bfloat16_rn(acc.y * inv);
         dst[2] = __float2bfloat16_rn(acc.z * inv);
