@@ -270,3 +270,18 @@ def test_generation_one_step_ahead_equals_step_by_step(setups, graphs, temperatu
         assert any(len(o) < max_new for o in a) or max_new == 1
         for o in a:
             assert not set(o) & set(stop_ids) and len(o) <= max_new
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+@pytest.mark.parametrize("batch", [12, 20])
+def test_decode_in_wider_batches(setups, name, dtype, batch):
+    """Twelve sequences (two token tiles of the few-token products) and twenty (the many-token products
+    take over): unequal prompts together, then token by token, against the plain implementation."""
+    _, config, weights, model = setups[(name, dtype)]
+    V = config["vocab_size"]
+    g = torch.Generator().manual_seed(batch)
+    lengths = [int(x) for x in torch.randint(3, 40, (batch,), generator=g)]
+    prompts = random_prompts(V, lengths, seed=70 + batch)
+    eng = bb.Engine(model, max_tokens=64 * batch, max_slots=batch)
+    run_batch_teacher_forced(eng, config, weights, prompts, [max(1, n - 4) for n in lengths], dtype)
+    assert eng.cache.live_slots == 0
