@@ -520,7 +520,9 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor,
     (bfloat16, head_dim <= 256, group <= 16, pages of 64 keys).  With more than
     one split the partial results go through float32 scratch: ``scratch`` =
     (part_o [batch * n_q * n_splits * head_dim], part_ml [batch * n_q * n_splits * 2]),
-    made here when it is not given."""
+    made here when it is not given.  ``cu_q``, ``kv_len`` and ``page_table`` are read before the kernel
+    waits for the launch before it (they are the host's description of the step, copied in before the
+    step's first kernel); ``q`` and the pages are read after."""
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16
     assert q.stride(-1) == 1 and out.stride(-1) == 1 and k_pages.is_contiguous() and v_pages.is_contiguous()
     assert tuple(k_pages.shape[1:]) == (n_kv, page_size, head_dim)
