@@ -274,6 +274,7 @@ def skinny_qkv_rope(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, po
 
 
 USE_TC_GEMM = True      # False: many-token bfloat16 products go to the library (cuBLAS) instead
+USE_PAIR_GEMM = True    # False: the tcgen05 product runs one block per tile instead of a pair of SMs per tile
 
 
 def gemm_tc_ok(x: torch.Tensor, weight: torch.Tensor, gated: bool = False, sms: int = 148) -> bool:
@@ -289,8 +290,11 @@ def gemm_tc_ok(x: torch.Tensor, weight: torch.Tensor, gated: bool = False, sms: 
 
 
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "store",
-            activation: str = "gelu_tanh") -> None:
+            activation: str = "gelu_tanh", pairs: Optional[bool] = None) -> None:
     """out = x @ weight^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulation in tensor memory).
+
+    Runs on pairs of SMs (``gemm_tc2``: 256 x 256 tiles, tcgen05 cta_group::2) unless ``pairs`` is False or
+    ``USE_PAIR_GEMM`` is off; then one block per 128 x 256 tile.
 
     ``epilogue``: "store" (out bfloat16 or float32) or "gated" (weight = [Wg; Wu], out = act(x Wg^T) * (x Wu^T),
     out width a multiple of 128)."""
@@ -301,16 +305,46 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: 
     assert weight.shape == ((2 * N if code else N), K) and out.shape[0] == M
     if activation not in ACTIVATIONS:
         raise KernelError(f"gemm_tc: unknown activation '{activation}'")
+    if USE_PAIR_GEMM and pairs is not False:
+        return gemm_tc2(x, weight, out, epilogue, activation)
     f = _fn("gemm_tc", "brolm_gemm_tc", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                          c_int, c_int, c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K, code,
              1 if out.dtype == torch.float32 else 0, ACTIVATIONS[activation], _stream()), "gemm_tc")
 
 
+def gemm_tc2(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "store",
+             activation: str = "gelu_tanh") -> None:
+    """``gemm_tc`` on pairs of SMs (tcgen05 cta_group::2): 256 x 256 tiles, each block of a pair loads half
+    of the weight tile.  Same operands and epilogues."""
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    assert weight.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == x.shape[0]
+    M, K = x.shape
+    code = {"store": 0, "gated": 1}[epilogue]
+    N = out.shape[1]
+    assert weight.shape == ((2 * N if code == 1 else N), K)
+    f = _fn("gemm_tc2", "brolm_gemm_tc2", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                           c_int, c_int, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K, code,
+             1 if out.dtype == torch.float32 else 0, ACTIVATIONS[activation], _stream()), "gemm_tc2")
+
+
+def gemm_tc2_status(reset: bool = False) -> int:
+    """0 if no bounded wait inside gemm_tc2 ever ran out; otherwise its code.  Synchronises."""
+    if not library_loaded("gemm_tc2"):
+        return 0
+    f = load_library("gemm_tc2").brolm_gemm_tc2_status
+    f.argtypes = [c_int]
+    f.restype = c_int
+    return f(1 if reset else 0)
+
+
 def gemm_tc_status(reset: bool = False) -> int:
-    """0 if no bounded wait inside gemm_tc ever ran out; otherwise the code of the first one.  Synchronises."""
-    if not library_loaded("gemm_tc"):
-        return 0                   # none of its kernels ever ran: nothing is built or loaded for the question
+    """0 if no bounded wait inside gemm_tc (either form) ever ran out; otherwise the code of the first one.
+    Synchronises."""
+    pair = gemm_tc2_status(reset)
+    if pair or not library_loaded("gemm_tc"):
+        return pair                # (a library none of whose kernels ever ran is not built or loaded for the question)
     f = load_library("gemm_tc").brolm_gemm_tc_status
     f.argtypes = [c_int]
     f.restype = c_int
@@ -564,6 +598,6 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
 
 
 __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "embed_scale", "rmsnorm", "residual_rmsnorm",
-           "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts",
+           "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc2", "gemm_tc2_status", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts",
            "gemm_stream_status", "chain_make_map", "decode_chain", "decode_chain_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_tc_status", "attention_decode_mma",
            "decode_splits", "argmax", "sample"]

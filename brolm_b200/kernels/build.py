@@ -37,6 +37,7 @@ LIBRARIES: dict[str, list[str]] = {
     "skinny_gemm": ["skinny_gemm.cu"],
     "attn_noalloc": ["attn_decode_noalloc.cu"],
     "gemm_tc": ["gemm_tc.cu"],
+    "gemm_tc2": ["gemm_tc2.cu"],
     "attn_tc": ["attn_tc.cu"],
     "gemm_stream": ["gemm_stream.cu"],
     "decode_chain": ["decode_chain.cu"],

@@ -135,9 +135,11 @@ def gemm(args) -> None:
         out = torch.empty(T, n, dtype=torch.bfloat16, device=DEV)
         wide = torch.empty(T, rows, dtype=torch.bfloat16, device=DEV)
         ms = timed(lambda: gemm_tc(x, w, out, epi), args.reps)
+        one = timed(lambda: gemm_tc(x, w, out, epi, pairs=False), args.reps)
         lib = timed(lambda: torch.mm(x, w.t(), out=wide), args.reps)
         fl = 2.0 * T * rows * k
-        print(f"gemm_tc {name} M={T} N={rows} K={k}: {ms * 1e3:.1f} us, {fl / ms / 1e9:.0f} TFLOP/s "
+        print(f"gemm_tc {name} M={T} N={rows} K={k}: pairs of SMs {ms * 1e3:.1f} us, {fl / ms / 1e9:.0f} TFLOP/s; "
+              f"one block per tile {one * 1e3:.1f} us, {fl / one / 1e9:.0f} TFLOP/s "
               f"(library product alone, without the activation: {lib * 1e3:.1f} us, {fl / lib / 1e9:.0f} TFLOP/s)")
     print("gemm_tc status", gemm_tc_status())
 

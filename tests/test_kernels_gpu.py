@@ -176,28 +176,31 @@ def test_skinny_gemm_partial_sums_feed_the_residual_kernel(parts):
     assert kernels.skinny_parts(torch.empty(8, 2304), torch.empty(18432, 2304)) == 1
 
 
+@pytest.mark.parametrize("pairs", [True, False])
 @pytest.mark.parametrize("M,N,K", [(17, 256, 64), (128, 256, 256), (100, 300, 200), (333, 2304, 2048), (1000, 40, 72),
-                                   (2048, 512, 9216)])
-def test_gemm_tc(M, N, K):
+                                   (2048, 512, 9216), (257, 520, 136)])
+def test_gemm_tc(M, N, K, pairs):
+    """One block per 128 x 256 tile, and a pair of SMs per 256 x 256 tile (cta_group::2)."""
     g = torch.Generator().manual_seed(M + N + K)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
     ref = plain.linear(x, w)
     for dt in (torch.bfloat16, torch.float32):
         out = torch.full((M, N), 7.0, dtype=dt, device=DEV)
-        kernels.gemm_tc(x.to(DEV), w.to(DEV), out)
+        kernels.gemm_tc(x.to(DEV), w.to(DEV), out, pairs=pairs)
         close(out, ref, dt, scale=float(ref.abs().max()) * (50 if dt == torch.float32 else 1))
     assert kernels.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("pairs", [True, False])
 @pytest.mark.parametrize("M,F,K,act", [(17, 128, 64, "gelu_tanh"), (300, 384, 200, "silu"), (2048, 9216, 2304, "gelu_tanh")])
-def test_gemm_tc_gated(M, F, K, act):
+def test_gemm_tc_gated(M, F, K, act, pairs):
     g = torch.Generator().manual_seed(F + K)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
     w = (torch.randn(2 * F, K, generator=g) * 0.05).to(torch.bfloat16)
     xd, wd = x.to(DEV), w.to(DEV)
     out = torch.empty(M, F, dtype=torch.bfloat16, device=DEV)
-    kernels.gemm_tc(xd, wd, out, "gated", act)
+    kernels.gemm_tc(xd, wd, out, "gated", act, pairs=pairs)
     gate, up = xd.double() @ wd[:F].double().t(), xd.double() @ wd[F:].double().t()      # float64 on the device: fast
     ref = (plain.gelu_tanh(gate) if act == "gelu_tanh" else gate * torch.sigmoid(gate)) * up
     close(out, ref, torch.bfloat16)
