@@ -76,12 +76,12 @@ def attn_prefill(args) -> None:
     def run():
         attention_prefill_mma(qkv[:, :n_q * hd], out, cu, qkv[:, n_q * hd:(n_q + n_kv) * hd],
                               qkv[:, (n_q + n_kv) * hd:], n_kv=n_kv, group=n_q // n_kv, head_dim=hd,
-                              scale=1 / math.sqrt(hd), cap=50.0, window=args.window, batch=1, max_q_len=T)
+                              scale=1 / math.sqrt(hd), cap=args.cap, window=args.window, batch=1, max_q_len=T)
 
     def run_tc():
         attention_prefill_tc(qkv[:, :n_q * hd], out, cu, qkv[:, n_q * hd:(n_q + n_kv) * hd],
                              qkv[:, (n_q + n_kv) * hd:], n_kv=n_kv, group=n_q // n_kv, head_dim=hd,
-                             scale=1 / math.sqrt(hd), cap=50.0, window=args.window, batch=1, max_q_len=T)
+                             scale=1 / math.sqrt(hd), cap=args.cap, window=args.window, batch=1, max_q_len=T)
 
     w = args.window or T
     keys = sum(min(p + 1, w) for p in range(T))
@@ -235,6 +235,7 @@ def main() -> None:
     ap.add_argument("--head-dim", type=int, default=256)
     ap.add_argument("--hidden", type=int, default=2304)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--cap", type=float, default=50.0, help="soft cap of the attention scores (0: none)")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--no-tc", action="store_true", help="many-token products through the library instead of gemm_tc")
     args = ap.parse_args()
