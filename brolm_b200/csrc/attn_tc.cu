@@ -4,26 +4,26 @@
 // One block owns 128 rows of one (sequence, kv head); a row is a (query token,
 // query head of the group) pair, so the query heads that share a kv head share
 // every key/value tile.  Keys and values come from the packed projection output
-// of the step, 64 keys per tile.  Both products take their A operand from tensor
-// memory, so that shared memory carries only the key and value tiles (with the
-// queries and the probabilities in shared memory as well, the two products read
-// 144 KB of it per tile and its bandwidth set the pace):
+// of the step, 128 keys per tile (a tcgen05.mma of 128 rows costs the same 64
+// or so cycles for 64 as for 128 columns, so narrower score tiles waste half
+// of the first product's time):
 //
-//   warp 0    one thread issues the TMA loads: a three-stage ring of key tiles
-//             and one of value tiles (128-byte swizzle);
-//   warp 1    one thread issues tcgen05.mma: S = Q K^T (M 128, N 64, Q from tensor
-//             memory) into one of two score buffers in tensor memory, and
-//             O += P V (M 128, N head size, P from tensor memory) into the output
-//             accumulator in tensor memory; the values are used as they lie in
-//             memory (keys x head size, an MN-major operand): nothing is transposed;
-//   warps 2-9 softmax: two threads own each row, 32 of the tile's 64 scores
-//             each.  At the start a thread copies its half of the row's query
-//             from global memory into tensor memory (bfloat16 pairs, one per
-//             32-bit column).  Per tile it reads its scores with tcgen05.ld,
-//             applies scale, soft-cap and mask, agrees with its partner on the
-//             row's reference maximum, and writes the probabilities as bfloat16
-//             pairs over the first half of the score buffer (tcgen05.st); at the
-//             end it scales its half of the accumulator by 1 / sum and stores it.
+//   warp 0    one thread issues the TMA loads: the query tile once, then key
+//             and value units into one ring of shared-memory slots in the
+//             order in which the products use them (a key tile comes as two
+//             halves of the head size, a value tile as two halves of its keys,
+//             so a slot is free again as soon as its half is multiplied);
+//   warp 1    one thread issues tcgen05.mma: S = Q K^T (M 128, N 128) into one of
+//             two score buffers in tensor memory, and O += P V (M 128, N head
+//             size, P read from tensor memory) into the output accumulator in
+//             tensor memory; the values are used as they lie in memory (keys x
+//             head size, an MN-major operand): nothing is transposed;
+//   warps 2-9 softmax: two threads own each row, 64 of the tile's 128 scores
+//             each.  A thread reads its scores with tcgen05.ld, applies scale,
+//             soft-cap and mask, agrees with its partner on the row's reference
+//             maximum, writes the probabilities as bfloat16 pairs over the
+//             first half of the score buffer (tcgen05.st), and at the end
+//             scales its half of the accumulator by 1 / sum and stores it.
 //
 // The tensor core runs the products in the order of issue, which is what keeps
 // the score buffers safe: S(j+2) is issued after P(j) V(j), which read the same
@@ -44,8 +44,8 @@
 
 namespace {
 
-constexpr int BM = 128, BN = 64;
-constexpr int STAGES = 3;         // key tiles and value tiles in flight
+constexpr int BM = 128, BN = 128;
+constexpr int MAX_SLOTS = 8;
 constexpr int THREADS = 320;      // loader warp, issuer warp, eight softmax warps
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -54,8 +54,6 @@ constexpr float RESCALE_GAP = 8.0f;
 __device__ int g_attn_tc_error;
 
 struct TcArgs {
-    const bf16* q;
-    int q_stride;
     bf16* out;
     int out_stride;
     const int32_t* cu_q;
@@ -72,26 +70,39 @@ __device__ __forceinline__ bool wait_on(uint32_t bar, uint32_t parity, volatile 
 }
 __device__ __forceinline__ uint32_t idesc(int m, int n, int b_mn_major) { return idesc_bf16(m, n, b_mn_major); }
 
+// The shapes that depend on the head size.  A key tile is KU units (parts of the head size, all 128 keys), a
+// value tile two units (64 keys each, the whole head size); a ring slot holds either.
+template <int HD>
+struct Shape {
+    static constexpr int DB = HD / 64;                           // 64-wide blocks of the head size
+    static constexpr int KU = HD >= 128 ? 2 : 1;
+    static constexpr int K_BOXES = DB / KU;                      // blocks of the head size in a key unit
+    static constexpr int K_UNIT = BN * (HD / KU) * 2, V_UNIT = 64 * HD * 2;
+    static constexpr int SLOT = K_UNIT > V_UNIT ? K_UNIT : V_UNIT;
+    static constexpr int SLOTS = HD == 256 ? 5 : MAX_SLOTS;
+    static constexpr int Q_BYTES = BM * HD * 2;
+};
+
 // barrier slots
-enum : int { Q_FULL = 0, K_FULL = 1, K_EMPTY = K_FULL + STAGES, V_FULL = K_EMPTY + STAGES, V_EMPTY = V_FULL + STAGES,
-             S_FULL = V_EMPTY + STAGES, P_FULL = S_FULL + 2, PV_DONE = P_FULL + 2, N_BARS = PV_DONE + 2 };
+enum : int { Q_FULL = 0, S_FULL = 1, P_FULL = 3, PV_DONE = 5, U_FULL = 7, U_EMPTY = U_FULL + MAX_SLOTS,
+             N_BARS = U_EMPTY + MAX_SLOTS };
 
 template <int HD>
-__global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
+__global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                     const __grid_constant__ CUtensorMap map_k,
                                                                      const __grid_constant__ CUtensorMap map_v, TcArgs a) {
-    constexpr int DB = HD / 64;                          // 64-wide blocks of the head size
-    constexpr int KV_BYTES = BN * HD * 2;
-    // tensor-memory columns: two score buffers (the probabilities go over their first halves), the output, the queries
-    constexpr uint32_t S_COL = 0, O_COL = 2 * BN, Q_COL = O_COL + HD;
-    static_assert(Q_COL + HD / 2 <= TMEM_COLS, "tensor memory");
+    using SH = Shape<HD>;
+    constexpr int DB = SH::DB, KU = SH::KU, SLOTS = SH::SLOTS;
+    constexpr uint32_t S_COL = 0, O_COL = 2 * BN;        // tensor-memory columns: two score buffers, then the output
+    static_assert(O_COL + HD <= TMEM_COLS, "tensor memory");
     extern __shared__ __align__(1024) uint8_t smem_raw[];     // the swizzled tiles need 1024-byte alignment
     uint8_t* base = smem_raw;
     if ((smem_u32(base) & 1023u) != 0) {                      // never seen; refuse rather than compute wrongly
         if (threadIdx.x == 0) atomicCAS(&g_attn_tc_error, 0, 13);
         return;
     }
-    const uint32_t k_s = smem_u32(base), v_s = k_s + STAGES * KV_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base + 2 * STAGES * KV_BYTES);
+    const uint32_t q_s = smem_u32(base), ring = q_s + SH::Q_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + SH::Q_BYTES + SLOTS * SH::SLOT);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
     volatile int* give_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars + N_BARS) + 16);   // [2][2][BM]: maxima by tile parity and half; the sums reuse it
@@ -116,17 +127,15 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
     const int n_tiles = active ? tok_hi / BN - t_first + 1 : 0;
 
     if (threadIdx.x == 0) {
-        mbar_init(bar(Q_FULL), 8);
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar(K_FULL + s), 1);
-            mbar_init(bar(K_EMPTY + s), 1);
-            mbar_init(bar(V_FULL + s), 1);
-            mbar_init(bar(V_EMPTY + s), 1);
-        }
+        mbar_init(bar(Q_FULL), 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(bar(S_FULL + s), 1);
             mbar_init(bar(P_FULL + s), 8);
             mbar_init(bar(PV_DONE + s), 1);
+        }
+        for (int s = 0; s < SLOTS; ++s) {
+            mbar_init(bar(U_FULL + s), 1);
+            mbar_init(bar(U_EMPTY + s), 1);
         }
         give_up[0] = 0;
         give_up[1] = 0;
@@ -140,111 +149,113 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
     fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
+    // Units go through the ring in the order of their use: K(0); then K(j+1), V(j) for every tile j.
     if (warp == 0) {
         if (lane == 0 && n_tiles > 0) {
-            int issued_k = 0, issued_v = 0;
+            mbar_expect_tx(bar(Q_FULL), SH::Q_BYTES);
+            for (int d = 0; d < DB; ++d)
+                tma_load_3d(q_s + d * (BM * 128), &map_q, d * 64, g * a.group, q0 + tok0, bar(Q_FULL));
+            int u = 0;
             bool ok = true;
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int st = j % STAGES;
-                const uint32_t ph = (j / STAGES) & 1;
+            auto slot_free = [&]() -> bool {
+                ok = wait_on(bar(U_EMPTY + u % SLOTS), ((u / SLOTS) & 1) ^ 1, give_up, 1);
+                return ok;
+            };
+            auto load_k = [&](int j) {
                 const int key0 = q0 + (t_first + j) * BN;
-                ok = wait_on(bar(K_EMPTY + st), ph ^ 1, give_up, 1);
-                if (!ok) break;
-                mbar_expect_tx(bar(K_FULL + st), KV_BYTES);
-                for (int d = 0; d < DB; ++d)
-                    tma_load_3d(k_s + st * KV_BYTES + d * (BN * 128), &map_k, d * 64, g, key0, bar(K_FULL + st));
-                ++issued_k;
-                ok = wait_on(bar(V_EMPTY + st), ph ^ 1, give_up, 2);
-                if (!ok) break;
-                mbar_expect_tx(bar(V_FULL + st), KV_BYTES);
-                for (int d = 0; d < DB; ++d)
-                    tma_load_3d(v_s + st * KV_BYTES + d * (BN * 128), &map_v, d * 64, g, key0, bar(V_FULL + st));
-                ++issued_v;
+                for (int ku = 0; ku < KU && ok; ++ku) {
+                    if (!slot_free()) return;
+                    const int sl = u % SLOTS;
+                    mbar_expect_tx(bar(U_FULL + sl), SH::K_UNIT);
+                    for (int d = 0; d < SH::K_BOXES; ++d)
+                        tma_load_3d(ring + sl * SH::SLOT + d * (BN * 128), &map_k, (ku * SH::K_BOXES + d) * 64, g, key0,
+                                    bar(U_FULL + sl));
+                    ++u;
+                }
+            };
+            auto load_v = [&](int j) {
+                const int key0 = q0 + (t_first + j) * BN;
+                for (int vu = 0; vu < 2 && ok; ++vu) {
+                    if (!slot_free()) return;
+                    const int sl = u % SLOTS;
+                    mbar_expect_tx(bar(U_FULL + sl), SH::V_UNIT);
+                    for (int d = 0; d < DB; ++d)
+                        tma_load_3d(ring + sl * SH::SLOT + d * (64 * 128), &map_v, d * 64, g, key0 + vu * 64, bar(U_FULL + sl));
+                    ++u;
+                }
+            };
+            load_k(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) load_k(j + 1);
+                if (ok) load_v(j);
             }
             if (*give_up) {        // let the loads in flight land before the block goes away
-                for (int j = max(0, issued_k - STAGES); j < issued_k; ++j)
-                    wait_on(bar(K_FULL + j % STAGES), (j / STAGES) & 1, give_up + 1, 9);
-                for (int j = max(0, issued_v - STAGES); j < issued_v; ++j)
-                    wait_on(bar(V_FULL + j % STAGES), (j / STAGES) & 1, give_up + 1, 9);
+                wait_on(bar(Q_FULL), 0, give_up + 1, 9);
+                for (int i = max(0, u - SLOTS); i < u; ++i) wait_on(bar(U_FULL + i % SLOTS), (i / SLOTS) & 1, give_up + 1, 9);
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && n_tiles > 0) {
             const uint32_t id_qk = idesc(BM, BN, 0), id_pv = idesc(BM, HD, 1);
             bool ok = wait_on(bar(Q_FULL), 0, give_up, 3);
-            fence_after_sync();
+            int u = 0;
             // S(j) goes over the buffer that P(j-2) was read from: the product that read it was issued before
             auto issue_qk = [&](int j) -> bool {
-                const int s = j & 1, st = j % STAGES;
-                if (!wait_on(bar(K_FULL + st), (j / STAGES) & 1, give_up, 4)) return false;
-                fence_after_sync();
+                const int s = j & 1;
 #pragma unroll
-                for (int d = 0; d < DB; ++d) {
-                    const uint64_t kb = desc_kmajor(k_s + st * KV_BYTES + d * (BN * 128));
+                for (int ku = 0; ku < KU; ++ku) {
+                    const int sl = u % SLOTS;
+                    if (!wait_on(bar(U_FULL + sl), (u / SLOTS) & 1, give_up, 4)) return false;
+                    fence_after_sync();
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma_ts(tmem + S_COL + s * BN, tmem + Q_COL + (d * 4 + k) * 8, kb + 2 * k, id_qk, (d | k) != 0);
+                    for (int d = 0; d < SH::K_BOXES; ++d) {
+                        const uint64_t qa = desc_kmajor(q_s + (ku * SH::K_BOXES + d) * (BM * 128));
+                        const uint64_t kb = desc_kmajor(ring + sl * SH::SLOT + d * (BN * 128));
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            umma(tmem + S_COL + s * BN, qa + 2 * k, kb + 2 * k, id_qk, (ku | d | k) != 0);
+                    }
+                    umma_commit(bar(U_EMPTY + sl));
+                    ++u;
                 }
                 umma_commit(bar(S_FULL + s));
-                umma_commit(bar(K_EMPTY + st));
                 return true;
             };
             if (ok) ok = issue_qk(0);
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles) { ok = issue_qk(j + 1); if (!ok) break; }
-                const int s = j & 1, st = j % STAGES;
-                ok = wait_on(bar(P_FULL + s), (j >> 1) & 1, give_up, 6) && wait_on(bar(V_FULL + st), (j / STAGES) & 1, give_up, 7);
+                const int s = j & 1;
+                ok = wait_on(bar(P_FULL + s), (j >> 1) & 1, give_up, 6);
                 if (!ok) break;
-                fence_after_sync();
 #pragma unroll
-                for (int k = 0; k < BN / 16; ++k) {
-                    // sixteen keys further: eight columns of P, sixteen 128-byte rows down in V
-                    const uint64_t vb = desc_mnmajor(v_s + st * KV_BYTES + k * (16 * 128), a.v_lbo, a.v_sbo);
-                    umma_ts(tmem + O_COL, tmem + S_COL + s * BN + k * 8, vb, id_pv, (j | k) != 0);
+                for (int vu = 0; vu < 2; ++vu) {
+                    const int sl = u % SLOTS;
+                    ok = wait_on(bar(U_FULL + sl), (u / SLOTS) & 1, give_up, 7);
+                    if (!ok) break;
+                    fence_after_sync();
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        // sixteen keys further: eight columns of P, sixteen 128-byte rows down in V
+                        const uint64_t vb = desc_mnmajor(ring + sl * SH::SLOT + k * (16 * 128), a.v_lbo, a.v_sbo);
+                        umma_ts(tmem + O_COL, tmem + S_COL + s * BN + (vu * 4 + k) * 8, vb, id_pv, (j | vu | k) != 0);
+                    }
+                    umma_commit(bar(U_EMPTY + sl));
+                    ++u;
                 }
-                umma_commit(bar(V_EMPTY + st));
+                if (!ok) break;
                 umma_commit(bar(PV_DONE + s));
             }
         }
     } else if (n_tiles > 0) {
         // Two warps share each quarter of the rows (a warp may only touch the 32 lanes of tensor memory of its
-        // quarter): warp w and warp w + 4 own the same 32 rows, the first takes score columns 0-31, the second
-        // 32-63.  They agree on the row's reference maximum through shared memory and a 64-thread barrier.
+        // quarter): warp w and warp w + 4 own the same 32 rows, the first takes score columns 0-63, the second
+        // 64-127.  They agree on the row's reference maximum through shared memory and a 64-thread barrier.
+        constexpr int W = BN / 2;                           // scores of a thread per tile
         const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;                  // this thread's row of the block
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const bool row_ok = r < rows_here;
-        const int row = row0 + r, tok = row / a.group, head = g * a.group + row % a.group;
-        const int pos = tok;                                // position of the row's token (prompts start at 0)
-        {
-            // this thread's half of the row's query: HD / 2 values, HD / 4 columns
-            const uint4* src = reinterpret_cast<const uint4*>(a.q + (size_t)(q0 + tok) * a.q_stride + (size_t)head * HD + half * (HD / 2));
-            constexpr int COLS = HD / 4;
-            if constexpr (COLS >= 32) {
-#pragma unroll 1
-                for (int c = 0; c < COLS; c += 32) {
-                    uint32_t qv[32];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const uint4 t = row_ok ? __ldg(src + c / 4 + i) : make_uint4(0, 0, 0, 0);
-                        qv[4 * i] = t.x; qv[4 * i + 1] = t.y; qv[4 * i + 2] = t.z; qv[4 * i + 3] = t.w;
-                    }
-                    tmem_st32(tmem + lane_addr + Q_COL + half * COLS + c, qv);
-                }
-            } else {
-                uint32_t qv[16];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const uint4 t = row_ok ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
-                    qv[4 * i] = t.x; qv[4 * i + 1] = t.y; qv[4 * i + 2] = t.z; qv[4 * i + 3] = t.w;
-                }
-                tmem_st16(tmem + lane_addr + Q_COL + half * COLS, qv);
-            }
-            tmem_wait_st();
-            fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(Q_FULL));
-        }
+        const int pos = tok0 + r / a.group;                 // position of the row's token (prompts start at 0)
         const float c0 = a.cap > 0.0f ? a.scale / a.cap * (2.0f * LOG2E) : a.scale * LOG2E;
         const float c1 = a.cap * LOG2E, c2 = 2.0f * a.cap * LOG2E;
         float m_ref = -INFINITY, l = 0.0f;                  // l: the sum over this thread's columns only
@@ -254,35 +265,40 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
             ok = wait_on(bar(S_FULL + s), (j >> 1) & 1, give_up, 8);
             if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
             fence_after_sync();
-            uint32_t sv[32];
-            tmem_ld32(tmem + lane_addr + S_COL + s * BN + half * 32, sv);
+            uint32_t sv[W];
+            {
+                uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[0]);
+                uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[32]);
+                tmem_ld32(tmem + lane_addr + S_COL + s * BN + half * W, lo);
+                tmem_ld32(tmem + lane_addr + S_COL + s * BN + half * W + 32, hi);
+            }
             tmem_wait_ld();
 
             const int key_base = (t_first + j) * BN;
             const bool edge = key_base + BN - 1 > tok0 || key_base < tok_hi - window + 1;
             // score in log2 units: with the cap,  cap log2e tanh(x) = c1 - c2 / (1 + 2^(s c0));  without,  s c0
-            float sc[32];
+            float sc[W];
             float m_t = -INFINITY;
             if (a.cap > 0.0f) {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
+                for (int c = 0; c < W; ++c) {
                     const float t = fast_exp2(__uint_as_float(sv[c]) * c0);
                     sc[c] = fmaf(-c2, fast_rcp(1.0f + t), c1);
                 }
             } else {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) sc[c] = __uint_as_float(sv[c]) * c0;
+                for (int c = 0; c < W; ++c) sc[c] = __uint_as_float(sv[c]) * c0;
             }
             if (edge) {
-                const int kp0 = key_base + half * 32;
+                const int kp0 = key_base + half * W;
                 // visible: kp <= pos and pos - kp < window, i.e. lo <= c <= hi for column c of this thread
                 const int hi = row_ok ? pos - kp0 : -1, lo = pos - window + 1 - kp0;
 #pragma unroll
-                for (int c = 0; c < 32; ++c)
+                for (int c = 0; c < W; ++c)
                     if (c > hi || c < lo) sc[c] = -INFINITY;
             }
 #pragma unroll
-            for (int c = 0; c < 32; ++c) m_t = fmaxf(m_t, sc[c]);
+            for (int c = 0; c < W; ++c) m_t = fmaxf(m_t, sc[c]);
             float* slot = xch + (s * 2 + half) * BM + r;    // double-buffered by the tile's parity
             *slot = m_t;
             // after this barrier both threads of the row hold their scores in registers, so the probabilities
@@ -313,19 +329,19 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
             }
             l *= corr;
             m_ref = m_new;
-            // probabilities -> tensor memory, bfloat16 pairs: keys 2c, 2c+1 of this thread in column c of its sixteen
+            // probabilities -> tensor memory, bfloat16 pairs: keys 2c, 2c+1 of this thread in column c of its 32
             float sum = 0.0f;
             const float m_sub = m_ref > -INFINITY ? m_ref : 0.0f;     // a row that has seen nothing: 2^(-inf - 0) = 0
-            uint32_t pw[16];
+            uint32_t pw[W / 2];
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
+            for (int c = 0; c < W / 2; ++c) {
                 const float p0 = fast_exp2(sc[2 * c] - m_sub), p1 = fast_exp2(sc[2 * c + 1] - m_sub);
                 sum += p0 + p1;
                 __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
                 pw[c] = *reinterpret_cast<uint32_t*>(&t);
             }
             l += sum;
-            tmem_st16(tmem + lane_addr + S_COL + s * BN + half * 16, pw);
+            tmem_st32(tmem + lane_addr + S_COL + s * BN + half * (W / 2), pw);
             tmem_wait_st();
             fence_before_sync();
             __syncwarp();
@@ -343,6 +359,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
             fence_after_sync();
             const float total = xch[fin * BM + r] + xch[(fin + 1) * BM + r];
             const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+            const int row = row0 + r, tok = row / a.group, head = g * a.group + row % a.group;
             bf16* dst = a.out + (size_t)(q0 + tok) * a.out_stride + (size_t)head * HD;
 #pragma unroll 1
             for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
@@ -380,15 +397,18 @@ int make_map(CUtensorMap* map, const void* ptr, long long tokens, int heads, int
 }
 
 template <int HD>
-int launch(const CUtensorMap& mk, const CUtensorMap& mv, const TcArgs& a, dim3 grid, cudaStream_t stream) {
-    constexpr size_t smem = 2 * STAGES * (size_t)BN * HD * 2 + N_BARS * 8 + 16 + 4 * BM * 4;
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcArgs& a, dim3 grid,
+           cudaStream_t stream) {
+    using SH = Shape<HD>;
+    constexpr size_t smem = (size_t)SH::Q_BYTES + (size_t)SH::SLOTS * SH::SLOT + N_BARS * 8 + 16 + 4 * BM * 4;
+    static_assert(smem <= 232448, "shared memory of a block");
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
-    attn_prefill_tc_kernel<HD><<<grid, THREADS, smem, stream>>>(mk, mv, a);
+    attn_prefill_tc_kernel<HD><<<grid, THREADS, smem, stream>>>(mq, mk, mv, a);
     return launch_status();
 }
 
@@ -406,21 +426,22 @@ BROLM_API int brolm_attn_prefill_tc(const void* q, int q_stride, void* out, int 
     if (group <= 0 || BM % group != 0 || n_kv <= 0 || batch > 65535 || n_kv > 65535) return BROLM_ERR_BAD_SIZE;
     if (q_stride % 8 || kv_stride % 8 || out_stride % 8) return BROLM_ERR_ALIGNMENT;
     if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) || ((uintptr_t)out & 15)) return BROLM_ERR_ALIGNMENT;
-    CUtensorMap mk, mv;
-    int st = make_map(&mk, k, total_tokens, n_kv, hd, kv_stride, 1, BN);
+    CUtensorMap mq, mk, mv;
+    int st = make_map(&mq, q, total_tokens, n_kv * group, hd, q_stride, group, BM / group);
     if (st) return st;
-    st = make_map(&mv, v, total_tokens, n_kv, hd, kv_stride, 1, BN);
+    st = make_map(&mk, k, total_tokens, n_kv, hd, kv_stride, 1, BN);      // a key unit: all keys of the tile
+    if (st) return st;
+    st = make_map(&mv, v, total_tokens, n_kv, hd, kv_stride, 1, 64);      // a value unit: 64 keys
     if (st) return st;
     TcArgs a;
-    a.q = (const bf16*)q; a.q_stride = q_stride;
     a.out = (bf16*)out; a.out_stride = out_stride; a.cu_q = (const int32_t*)cu_q;
     a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window;
-    a.v_lbo = (uint32_t)((v_lbo > 0 ? v_lbo : BN * 128) >> 4);      // next 64 head-size elements: the next box
+    a.v_lbo = (uint32_t)((v_lbo > 0 ? v_lbo : 64 * 128) >> 4);      // next 64 head-size elements: the next box
     a.v_sbo = (uint32_t)((v_sbo > 0 ? v_sbo : 1024) >> 4);          // next eight keys
     dim3 grid((max_q_len * group + BM - 1) / BM, n_kv, batch);
-    if (hd == 64) return launch<64>(mk, mv, a, grid, stream);
-    if (hd == 128) return launch<128>(mk, mv, a, grid, stream);
-    return launch<256>(mk, mv, a, grid, stream);
+    if (hd == 64) return launch<64>(mq, mk, mv, a, grid, stream);
+    if (hd == 128) return launch<128>(mq, mk, mv, a, grid, stream);
+    return launch<256>(mq, mk, mv, a, grid, stream);
 }
 
 BROLM_API int brolm_attn_tc_status(int reset) {
