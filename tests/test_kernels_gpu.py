@@ -386,6 +386,39 @@ def test_attention_packed(dtype, kernel, n_q, n_kv, hd, window, cap):
         t += n
 
 
+@pytest.mark.parametrize("n_q,n_kv,hd,window,cap,gain", [(8, 4, 256, 0, 50.0, 40.0), (4, 2, 64, 100, 30.0, 25.0),
+                                                         (4, 4, 128, 0, 20.0, 200.0)])
+def test_attention_tc_scores_beyond_the_cap(n_q, n_kv, hd, window, cap, gain):
+    """Queries scaled so that score * scale / cap runs from near 0 to far beyond 1: the tcgen05 kernel's
+    polynomial tanh (small scores) and its exact form (any large score in the warp's tile) both run, and
+    the sequences of length 300 and 700 have tiles of either kind."""
+    g = torch.Generator().manual_seed(5)
+    lengths = [300, 700, 129]
+    T = sum(lengths)
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * hd, generator=g)
+    # rows 0-255 of each sequence keep small scores; later query rows are large
+    t = 0
+    for n in lengths:
+        qkv[t + 256:t + n, :n_q * hd] *= gain
+        t += n
+    qkv = qkv.to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(hd)
+    dq = qkv.to(DEV)
+    out = torch.empty(T, n_q * hd, dtype=torch.bfloat16, device=DEV)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=DEV)
+    kernels.attention_prefill_tc(dq[:, :n_q * hd], out, cu, dq[:, n_q * hd:(n_q + n_kv) * hd], dq[:, (n_q + n_kv) * hd:],
+                                 n_kv=n_kv, group=n_q // n_kv, head_dim=hd, scale=scale, cap=cap, window=window,
+                                 batch=len(lengths), max_q_len=max(lengths))
+    assert kernels.attention_tc_status() == 0
+    t = 0
+    for n in lengths:
+        s = qkv[t:t + n]
+        ref = _attention_oracle(s[:, :n_q * hd], s[:, n_q * hd:(n_q + n_kv) * hd], s[:, (n_q + n_kv) * hd:],
+                                n_q, n_kv, hd, scale, cap, window)
+        close(out[t:t + n], ref, torch.bfloat16, scale=float(ref.abs().max()))
+        t += n
+
+
 def _paged_case(dtype, n_q, n_kv, hd, window, cap, lengths, page=64, special=None, seed=0, kernel="simt", splits=1):
     """Decode pass: one query per sequence over a scattered, possibly ring-shaped cache."""
     g = torch.Generator().manual_seed(seed)
