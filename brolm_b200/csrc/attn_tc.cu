@@ -261,9 +261,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
         const float c1 = a.cap * LOG2E, c2 = 2.0f * a.cap * LOG2E;
         // For |y| <= 1 (y = score * scale / cap, the usual case):  tanh(y) = y p(y^2)  with p of degree 5, fitted at
         // Chebyshev points of [0, 1]; its error of 5e-7 is that of the exact form's approximate instructions.
-        // The coefficients carry cap * log2(e).  small_exp: exponent bits of the largest power of two <= cap / scale.
+        // The coefficients carry cap * log2(e).  s_small: the largest |score| with |y| <= 1, rounding allowed for.
         const float cy = a.cap > 0.0f ? a.scale / a.cap : 0.0f;
-        const uint32_t small_exp = a.cap > 0.0f ? (__float_as_uint(a.cap / a.scale) & 0x7f800000u) : 0u;
+        const float s_small = a.cap > 0.0f ? 0.999f * a.cap / a.scale : 0.0f;
         const float k0 = c1 * TANH_P[0], k1 = c1 * TANH_P[1], k2 = c1 * TANH_P[2], k3 = c1 * TANH_P[3], k4 = c1 * TANH_P[4],
                     k5 = c1 * TANH_P[5];
         float m_ref = -INFINITY, l = 0.0f;                  // l: the sum over this thread's columns only
@@ -288,11 +288,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
             float sc[W];
             float m_t = -INFINITY;
             if (a.cap > 0.0f) {
-                // every |score| of the warp's tile below the power of two: the exponent bits of the OR say so
-                uint32_t any_bits = 0;
+                float s_max = 0.0f;                         // a NaN score turns up in the result either way
 #pragma unroll
-                for (int c = 0; c < W; ++c) any_bits |= sv[c];
-                if (__all_sync(0xffffffffu, (any_bits & 0x7f800000u) < small_exp)) {
+                for (int c = 0; c < W; ++c) s_max = fmaxf(s_max, fabsf(__uint_as_float(sv[c])));
+                if (__all_sync(0xffffffffu, s_max <= s_small)) {
                     // tanh as a polynomial on the FMA pipe; the special-function unit is left to the exponentials
 #pragma unroll
                     for (int c = 0; c < W; ++c) {
