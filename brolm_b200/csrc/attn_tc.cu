@@ -50,7 +50,6 @@ constexpr int THREADS = 320;      // loader warp, issuer warp, eight softmax war
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_GAP = 8.0f;
-__device__ constexpr float TANH_P[6] = {0.9999994039535522f, -0.3332895040512085f, 0.13280721008777618f, -0.05158598721027374f, 0.016720855608582497f, -0.0030582291074097157f};
 
 __device__ int g_attn_tc_error;
 
@@ -70,46 +69,6 @@ __device__ __forceinline__ bool wait_on(uint32_t bar, uint32_t parity, volatile 
     return mbar_wait(bar, parity, give_up, &g_attn_tc_error, code);
 }
 __device__ __forceinline__ uint32_t idesc(int m, int n, int b_mn_major) { return idesc_bf16(m, n, b_mn_major); }
-
-// Scores in log2 units.  With the cap:  cap log2e tanh(y),  y = score * scale / cap,  either exactly as
-// c1 - c2 / (1 + 2^(score c0)),  or, for |y| <= 1 (the usual case),  tanh(y) = y p(y^2)  with p of degree 5 fitted at
-// Chebyshev points of [0, 1] (its error of 5e-7 is that of the exact form's approximate instructions), which
-// leaves the special-function unit to the exponentials.  k[] carry cap * log2(e).  Without the cap:  score c0.
-// s_small: the largest |score| with |y| <= 1, rounding allowed for.
-struct CapConsts {
-    float c0, c1, c2, cy, s_small, k[6];
-};
-
-// One pass over a thread's W scores of a tile: soft cap (MODE 0 none, 1 polynomial, 2 exact), mask (EDGE: column c is
-// visible iff lo <= c <= hi), the maximum, and the probabilities 2^(score - m_sub) as bfloat16 pairs with their sum.
-template <int MODE, bool EDGE, int W>
-__device__ __forceinline__ void score_pass(const uint32_t (&sv)[W], float (&sc)[W], uint32_t (&pw)[W / 2], float& m_t,
-                                           float& sum, float m_sub, const CapConsts& cc, int lo, int hi) {
-#pragma unroll
-    for (int c = 0; c < W; c += 2) {
-        float v[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            const float x = __uint_as_float(sv[c + e]);
-            if constexpr (MODE == 1) {
-                const float y = x * cc.cy, u = y * y;
-                v[e] = y * fmaf(u, fmaf(u, fmaf(u, fmaf(u, fmaf(u, cc.k[5], cc.k[4]), cc.k[3]), cc.k[2]), cc.k[1]), cc.k[0]);
-            } else if constexpr (MODE == 2) {
-                v[e] = fmaf(-cc.c2, tc::fast_rcp(1.0f + tc::fast_exp2(x * cc.c0)), cc.c1);
-            } else {
-                v[e] = x * cc.c0;
-            }
-            if constexpr (EDGE)
-                if (c + e > hi || c + e < lo) v[e] = -INFINITY;
-            sc[c + e] = v[e];
-        }
-        m_t = fmaxf(m_t, fmaxf(v[0], v[1]));
-        const float p0 = tc::fast_exp2(v[0] - m_sub), p1 = tc::fast_exp2(v[1] - m_sub);
-        sum += p0 + p1;
-        __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
-        pw[c / 2] = *reinterpret_cast<uint32_t*>(&t);
-    }
-}
 
 // The shapes that depend on the head size.  A key tile is KU units (parts of the head size, all 128 keys), a
 // value tile two units (64 keys each, the whole head size); a ring slot holds either.
@@ -297,14 +256,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const bool row_ok = r < rows_here;
         const int pos = tok0 + r / a.group;                 // position of the row's token (prompts start at 0)
-        CapConsts cc;
-        cc.c0 = a.cap > 0.0f ? a.scale / a.cap * (2.0f * LOG2E) : a.scale * LOG2E;
-        cc.c1 = a.cap * LOG2E;
-        cc.c2 = 2.0f * a.cap * LOG2E;
-        cc.cy = a.cap > 0.0f ? a.scale / a.cap : 0.0f;
-        cc.s_small = a.cap > 0.0f ? 0.999f * a.cap / a.scale : 0.0f;
-#pragma unroll
-        for (int i = 0; i < 6; ++i) cc.k[i] = cc.c1 * TANH_P[i];
+        const float c0 = a.cap > 0.0f ? a.scale / a.cap * (2.0f * LOG2E) : a.scale * LOG2E;
+        const float c1 = a.cap * LOG2E, c2 = 2.0f * a.cap * LOG2E;
         float m_ref = -INFINITY, l = 0.0f;                  // l: the sum over this thread's columns only
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
@@ -323,31 +276,29 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
 
             const int key_base = (t_first + j) * BN;
             const bool edge = key_base + BN - 1 > tok0 || key_base < tok_hi - window + 1;
-            // visible: kp <= pos and pos - kp < window, i.e. lo <= c <= hi for column c of this thread
-            const int kp0 = key_base + half * W;
-            const int hi = row_ok ? pos - kp0 : -1, lo = pos - window + 1 - kp0;
-            int mode = 0;
-            if (a.cap > 0.0f) {
-                float s_max = 0.0f;                         // a NaN score turns up in the result either way
-#pragma unroll
-                for (int c = 0; c < W; ++c) s_max = fmaxf(s_max, fabsf(__uint_as_float(sv[c])));
-                mode = __all_sync(0xffffffffu, s_max <= cc.s_small) ? 1 : 2;
-            }
-            // One pass: scores in log2 units, their maximum, and the probabilities against the reference the row
-            // had before this tile, which is right unless the tile raises it (then they are computed again below).
+            // score in log2 units: with the cap,  cap log2e tanh(x) = c1 - c2 / (1 + 2^(s c0));  without,  s c0
             float sc[W];
-            uint32_t pw[W / 2];
-            float m_t = -INFINITY, sum = 0.0f;
-            const float m_before = m_ref > -INFINITY ? m_ref : 0.0f;
-            if (!edge) {
-                if (mode == 1) score_pass<1, false, W>(sv, sc, pw, m_t, sum, m_before, cc, lo, hi);
-                else if (mode == 2) score_pass<2, false, W>(sv, sc, pw, m_t, sum, m_before, cc, lo, hi);
-                else score_pass<0, false, W>(sv, sc, pw, m_t, sum, m_before, cc, lo, hi);
+            float m_t = -INFINITY;
+            if (a.cap > 0.0f) {
+#pragma unroll
+                for (int c = 0; c < W; ++c) {
+                    const float t = fast_exp2(__uint_as_float(sv[c]) * c0);
+                    sc[c] = fmaf(-c2, fast_rcp(1.0f + t), c1);
+                }
             } else {
-                if (mode == 1) score_pass<1, true, W>(sv, sc, pw, m_t, sum, m_before, cc, lo, hi);
-                else if (mode == 2) score_pass<2, true, W>(sv, sc, pw, m_t, sum, m_before, cc, lo, hi);
-                else score_pass<0, true, W>(sv, sc, pw, m_t, sum, m_before, cc, lo, hi);
+#pragma unroll
+                for (int c = 0; c < W; ++c) sc[c] = __uint_as_float(sv[c]) * c0;
             }
+            if (edge) {
+                const int kp0 = key_base + half * W;
+                // visible: kp <= pos and pos - kp < window, i.e. lo <= c <= hi for column c of this thread
+                const int hi = row_ok ? pos - kp0 : -1, lo = pos - window + 1 - kp0;
+#pragma unroll
+                for (int c = 0; c < W; ++c)
+                    if (c > hi || c < lo) sc[c] = -INFINITY;
+            }
+#pragma unroll
+            for (int c = 0; c < W; ++c) m_t = fmaxf(m_t, sc[c]);
             float* slot = xch + (s * 2 + half) * BM + r;    // double-buffered by the tile's parity
             *slot = m_t;
             // after this barrier both threads of the row hold their scores in registers, so the probabilities
@@ -356,40 +307,39 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
             m_t = fmaxf(m_t, xch[(s * 2 + (half ^ 1)) * BM + r]);
             // raise the reference only when the tile goes well beyond it
             const bool raise = m_t > m_ref + RESCALE_GAP;       // also true for the first visible tile of a row
-            if (__any_sync(0xffffffffu, raise)) {
-                const float m_new = raise ? m_t : m_ref;
-                const float corr = (raise && m_ref > -INFINITY) ? fast_exp2(m_ref - m_new) : 1.0f;
-                if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                    // rare: the accumulator has to be at rest (the product of the tile before is done), then every
-                    // row of the warp is rescaled (rows that keep their reference multiply by 1); each warp of the
-                    // pair takes half of the head size
-                    ok = wait_on(bar(PV_DONE + (s ^ 1)), ((j - 1) >> 1) & 1, give_up, 12);
-                    if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-                    fence_after_sync();
+            const float m_new = raise ? m_t : m_ref;
+            const float corr = (raise && m_ref > -INFINITY) ? fast_exp2(m_ref - m_new) : 1.0f;
+
+            if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+                // rare: the accumulator has to be at rest (the product of the tile before is done), then every
+                // row of the warp is rescaled (rows that keep their reference multiply by 1); each warp of the
+                // pair takes half of the head size
+                ok = wait_on(bar(PV_DONE + (s ^ 1)), ((j - 1) >> 1) & 1, give_up, 12);
+                if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+                fence_after_sync();
 #pragma unroll 1
-                    for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
-                        uint32_t ov[32];
-                        tmem_ld32(tmem + lane_addr + O_COL + c, ov);
-                        tmem_wait_ld();
+                for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
+                    uint32_t ov[32];
+                    tmem_ld32(tmem + lane_addr + O_COL + c, ov);
+                    tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
-                        tmem_st32(tmem + lane_addr + O_COL + c, ov);
-                    }
-                }
-                l *= corr;
-                m_ref = m_new;
-                // the probabilities again, against the new reference (rows that kept theirs get the same values)
-                const float m_sub = m_ref > -INFINITY ? m_ref : 0.0f;     // a row that has seen nothing: 2^(-inf - 0) = 0
-                sum = 0.0f;
-#pragma unroll
-                for (int c = 0; c < W / 2; ++c) {
-                    const float p0 = fast_exp2(sc[2 * c] - m_sub), p1 = fast_exp2(sc[2 * c + 1] - m_sub);
-                    sum += p0 + p1;
-                    __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
-                    pw[c] = *reinterpret_cast<uint32_t*>(&t);
+                    for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                    tmem_st32(tmem + lane_addr + O_COL + c, ov);
                 }
             }
+            l *= corr;
+            m_ref = m_new;
             // probabilities -> tensor memory, bfloat16 pairs: keys 2c, 2c+1 of this thread in column c of its 32
+            float sum = 0.0f;
+            const float m_sub = m_ref > -INFINITY ? m_ref : 0.0f;     // a row that has seen nothing: 2^(-inf - 0) = 0
+            uint32_t pw[W / 2];
+#pragma unroll
+            for (int c = 0; c < W / 2; ++c) {
+                const float p0 = fast_exp2(sc[2 * c] - m_sub), p1 = fast_exp2(sc[2 * c + 1] - m_sub);
+                sum += p0 + p1;
+                __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
+                pw[c] = *reinterpret_cast<uint32_t*>(&t);
+            }
             l += sum;
             tmem_st32(tmem + lane_addr + S_COL + s * BN + half * (W / 2), pw);
             tmem_wait_st();

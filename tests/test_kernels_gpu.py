@@ -389,9 +389,9 @@ def test_attention_packed(dtype, kernel, n_q, n_kv, hd, window, cap):
 @pytest.mark.parametrize("n_q,n_kv,hd,window,cap,gain", [(8, 4, 256, 0, 50.0, 40.0), (4, 2, 64, 100, 30.0, 25.0),
                                                          (4, 4, 128, 0, 20.0, 200.0)])
 def test_attention_tc_scores_beyond_the_cap(n_q, n_kv, hd, window, cap, gain):
-    """Queries scaled so that score * scale / cap runs from near 0 to far beyond 1: the tcgen05 kernel's
-    polynomial tanh (small scores) and its exact form (any large score in the warp's tile) both run, and
-    the sequences of length 300 and 700 have tiles of either kind."""
+    """Queries scaled so that score * scale / cap runs from near 0 to far beyond 1, where tanh is flat and
+    the row's reference maximum sits at the cap: tiles with small scores and tiles with saturated ones
+    follow one another within a sequence."""
     g = torch.Generator().manual_seed(5)
     lengths = [300, 700, 129]
     T = sum(lengths)
