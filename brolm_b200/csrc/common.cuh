@@ -131,6 +131,8 @@ static inline int launch_status() {
 // The environment variable BROLM_NO_PDL=1 falls back to plain stream order.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// The 128-byte line at p on its way into the L1, holding no register.
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 
 static inline bool pdl_enabled() {
     static int on = -1;

@@ -117,6 +117,8 @@ static int vec_chunks(int hidden, const void* a, const void* b, const void* c, c
     const uintptr_t bits = (uintptr_t)a | (uintptr_t)b | (uintptr_t)c | (uintptr_t)d;
     if (hidden % 4 != 0 || (bits & 15)) return 0;
     if (hidden <= 1024) return 1;
+    if (hidden <= 2048) return 2;
+    if (hidden <= 3072) return 3;
     if (hidden <= 4096) return 4;
     if (hidden <= 8192) return 8;
     return 0;
@@ -129,6 +131,8 @@ static int rmsnorm_launch(const void* x, const void* rows, const void* w, float 
 #define BROLM_RMS(C) launch_pdl(rmsnorm_kernel<X, W, O, C>, dim3(n), dim3(256), 0, s, (const X*)x, (const int32_t*)rows, \
                                 (const W*)w, eps, offset, (O*)out, hidden)
     if (c == 1) return BROLM_RMS(1);
+    if (c == 2) return BROLM_RMS(2);
+    if (c == 3) return BROLM_RMS(3);
     if (c == 4) return BROLM_RMS(4);
     if (c == 8) return BROLM_RMS(8);
     return BROLM_RMS(0);
@@ -166,7 +170,7 @@ BROLM_API int brolm_rmsnorm(const void* x, int x_dtype, const void* rows, const 
 // y may come as n_parts partial sums, part_stride elements apart (the slices
 // of a product that was cut along K); they are added in order while loading.
 template <typename Y, typename W, typename O, int MAXC>
-__global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict__ h, const Y* __restrict__ y,
+__global__ void __launch_bounds__(256, (MAXC >= 1 && MAXC <= 3) ? 4 : 1) residual_rmsnorm_kernel(float* __restrict__ h, const Y* __restrict__ y,
                                                                int n_parts, long long part_stride,
                                                                const W* __restrict__ w_post, float eps_post,
                                                                float off_post, const W* __restrict__ w_next,
@@ -212,16 +216,15 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
         return;
     }
     constexpr int C = MAXC > 0 ? MAXC : 1;
-    float v[C][4], res[C][4], gp[C][4], gn[C][4];
-    // the gains are weights: fetched while the kernel before this one finishes
-#pragma unroll
-    for (int c = 0; c < C; ++c) {
-        const int i = (c * 256 + threadIdx.x) * 4;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) gp[c][e] = gn[c][e] = 0.0f;
-        if (i < hidden) {
-            if (w_post) load4(w_post + i, gp[c]);
-            if (w_next) load4(w_next + i, gn[c]);
+    float v[C][4], res[C][4];
+    // The gains are weights: brought into the L1 while the kernel before this one finishes, and read where
+    // they are used, so that they hold no registers meanwhile (with many rows the number of blocks that fit
+    // an SM, and with it the bytes in flight, is set by the registers).
+    {
+        const size_t line = (size_t)threadIdx.x * 128;
+        if (line < (size_t)hidden * sizeof(W)) {
+            if (w_post) prefetch_l1(reinterpret_cast<const char*>(w_post) + line);
+            if (w_next) prefetch_l1(reinterpret_cast<const char*>(w_next) + line);
         }
     }
     pdl_wait();
@@ -255,9 +258,13 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
         ss = block_sum_once(ss, scratch, 0);
         const float inv_post = rsqrtf(ss / (float)hidden + eps_post);
 #pragma unroll
-        for (int c = 0; c < C; ++c)
+        for (int c = 0; c < C; ++c) {
+            const int i = (c * 256 + threadIdx.x) * 4;
+            float g[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (i < hidden) load4(w_post + i, g);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) v[c][e] = v[c][e] * inv_post * (off_post + gp[c][e]);
+            for (int e = 0; e < 4; ++e) v[c][e] = v[c][e] * inv_post * (off_post + g[e]);
+        }
     }
     float ss2 = 0.0f;
 #pragma unroll
@@ -277,9 +284,10 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
     for (int c = 0; c < C; ++c) {
         const int i = (c * 256 + threadIdx.x) * 4;
         if (i < hidden) {
-            float o[4];
+            float g[4], o[4];
+            load4(w_next + i, g);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) o[e] = res[c][e] * inv_next * (off_next + gn[c][e]);
+            for (int e = 0; e < 4; ++e) o[e] = res[c][e] * inv_next * (off_next + g[e]);
             store4(dst + i, o);
         }
     }
@@ -294,6 +302,8 @@ static int residual_launch(void* h, const void* y, int n_parts, long long part_s
 #define BROLM_RES(C) launch_pdl(residual_rmsnorm_kernel<Y, W, O, C>, dim3(n), dim3(256), 0, s, (float*)h, (const Y*)y, \
         n_parts, part_stride, (const W*)w_post, eps_post, off_post, (const W*)w_next, eps_next, off_next, (O*)out, hidden)
     if (c == 1) return BROLM_RES(1);
+    if (c == 2) return BROLM_RES(2);
+    if (c == 3) return BROLM_RES(3);
     if (c == 4) return BROLM_RES(4);
     if (c == 8) return BROLM_RES(8);
     return BROLM_RES(0);
