@@ -293,12 +293,123 @@ __global__ void __launch_bounds__(256, (MAXC >= 1 && MAXC <= 3) ? 4 : 1) residua
     }
 }
 
+// The same for y in one part, with the row in shared memory instead of registers: cp.async brings y and the
+// residual straight into the block's own copy, every thread reads back only the elements it copied itself
+// (the mapping of elements to threads and the order of every sum are those of the kernel above), and with
+// about 32 registers eight blocks fit an SM, which is what keeps enough bytes in flight when there are
+// thousands of rows.  Dynamic shared memory: C * 1024 elements of Y, then C * 1024 floats.
+__device__ __forceinline__ void copy_async(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async(bf16* dst, const bf16* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+template <typename Y, typename W, typename O, int C>
+__global__ void __launch_bounds__(256, 8) residual_rmsnorm_rows_kernel(float* __restrict__ h, const Y* __restrict__ y,
+                                                                       const W* __restrict__ w_post, float eps_post,
+                                                                       float off_post, const W* __restrict__ w_next,
+                                                                       float eps_next, float off_next,
+                                                                       O* __restrict__ out, int hidden) {
+    __shared__ float scratch[64];
+    extern __shared__ __align__(16) unsigned char row_raw[];
+    Y* sy = reinterpret_cast<Y*>(row_raw);
+    float* sh = reinterpret_cast<float*>(row_raw + (size_t)C * 1024 * sizeof(Y));
+    const int r = blockIdx.x;
+    float* hr = h + (size_t)r * hidden;
+    const Y* yr = y + (size_t)r * hidden;
+    O* dst = out + (size_t)r * hidden;
+    pdl_trigger();
+    {
+        const size_t line = (size_t)threadIdx.x * 128;
+        if (line < (size_t)hidden * sizeof(W)) {
+            if (w_post) prefetch_l1(reinterpret_cast<const char*>(w_post) + line);
+            if (w_next) prefetch_l1(reinterpret_cast<const char*>(w_next) + line);
+        }
+    }
+    pdl_wait();
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int i = (c * 256 + threadIdx.x) * 4;
+        if (i < hidden) {
+            copy_async(sh + i, hr + i);
+            copy_async(sy + i, yr + i);
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    float inv_post = 1.0f;
+    if (w_post) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            const int i = (c * 256 + threadIdx.x) * 4;
+            float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (i < hidden) load4(sy + i, v);
+            ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+        }
+        ss = block_sum_once(ss, scratch, 0);
+        inv_post = rsqrtf(ss / (float)hidden + eps_post);
+    }
+    float ss2 = 0.0f;
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int i = (c * 256 + threadIdx.x) * 4;
+        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f}, res[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (i < hidden) {
+            load4(sy + i, v);
+            load4(sh + i, res);
+            if (w_post) {
+                float g[4];
+                load4(w_post + i, g);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[e] = v[e] * inv_post * (off_post + g[e]);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            res[e] += v[e];
+            ss2 += res[e] * res[e];
+        }
+        if (i < hidden) {
+            store4(hr + i, res);
+            if (w_next) store4(sh + i, res);
+        }
+    }
+    if (!w_next) return;
+    ss2 = block_sum_once(ss2, scratch, 1);
+    const float inv_next = rsqrtf(ss2 / (float)hidden + eps_next);
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int i = (c * 256 + threadIdx.x) * 4;
+        if (i < hidden) {
+            float res[4], g[4], o[4];
+            load4(sh + i, res);
+            load4(w_next + i, g);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = res[e] * inv_next * (off_next + g[e]);
+            store4(dst + i, o);
+        }
+    }
+}
+
 template <typename Y, typename W, typename O>
 static int residual_launch(void* h, const void* y, int n_parts, long long part_stride, const void* w_post, float eps_post, float off_post,
                            const void* w_next, float eps_next, float off_next, void* out, int n, int hidden,
                            cudaStream_t s) {
     int c = vec_chunks(hidden, h, y, w_post, w_next);
     if (c && (((uintptr_t)out & 15) || part_stride % 4 != 0)) c = 0;
+    if (n_parts == 1 && c >= 1 && c <= 4) {
+        // one part: the row in shared memory (whatever the number of rows, so that a row's bits do not
+        // depend on how many rows the launch has)
+#define BROLM_ROWS(C) launch_pdl(residual_rmsnorm_rows_kernel<Y, W, O, C>, dim3(n), dim3(256), \
+        (size_t)C * 1024 * (sizeof(Y) + sizeof(float)), s, (float*)h, (const Y*)y, (const W*)w_post, eps_post, off_post, \
+        (const W*)w_next, eps_next, off_next, (O*)out, hidden)
+        if (c == 1) return BROLM_ROWS(1);
+        if (c == 2) return BROLM_ROWS(2);
+        if (c == 3) return BROLM_ROWS(3);
+        return BROLM_ROWS(4);
+#undef BROLM_ROWS
+    }
 #define BROLM_RES(C) launch_pdl(residual_rmsnorm_kernel<Y, W, O, C>, dim3(n), dim3(256), 0, s, (float*)h, (const Y*)y, \
         n_parts, part_stride, (const W*)w_post, eps_post, off_post, (const W*)w_next, eps_next, off_next, (O*)out, hidden)
     if (c == 1) return BROLM_RES(1);
