@@ -10,6 +10,8 @@
 // counter-based uniform number instead of std::mt19937_64.
 #include "common.cuh"
 
+#include <algorithm>
+
 #include <float.h>
 
 namespace {
@@ -173,11 +175,77 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     if (threadIdx.x == 0) out[blockIdx.x] = chosen != 0x7fffffff ? chosen : max(last_kept, 0);
 }
 
+// The same result with several blocks per row, for a few rows of a large vocabulary (one block would
+// read a megabyte alone).  A block folds its part of the row, then offers (value, index) as one 64-bit key
+// whose order is: greater value first, then smaller index; the row's key is an atomic maximum, and the block
+// that arrives last writes the index and puts the row's key and counter back to zero, so that the launch
+// needs no memset before it (it can be captured in a graph).  The keys and counters are static: launches
+// that use them at the same time on different streams would disturb each other.
+constexpr int ARGMAX_MAX_ROWS = 1024;
+__device__ unsigned long long g_argmax_key[ARGMAX_MAX_ROWS];
+__device__ unsigned int g_argmax_count[ARGMAX_MAX_ROWS];
+
+__global__ void __launch_bounds__(THREADS) argmax_parts_kernel(const float* __restrict__ logits, int vocab,
+                                                               int32_t* __restrict__ out) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const int r = blockIdx.x, parts = gridDim.y;
+    const float4* row4 = reinterpret_cast<const float4*>(logits + (size_t)r * vocab);     // vocab % 4 == 0, aligned
+    const int n4 = vocab >> 2, per = (n4 + parts - 1) / parts;
+    const int lo = blockIdx.y * per, hi = min(n4, lo + per);
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+#pragma unroll 4
+    for (int i = lo + (int)threadIdx.x; i < hi; i += blockDim.x) {
+        const float4 v = row4[i];
+        const float vs[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (vs[e] > best) { best = vs[e]; idx = 4 * i + e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sv[warp] = best; si[warp] = idx; }
+    __syncthreads();
+    if (warp != 0) return;
+    best = lane < (blockDim.x >> 5) ? sv[lane] : -INFINITY;
+    idx = lane < (blockDim.x >> 5) ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    if (lane != 0) return;
+    const unsigned int bits = __float_as_uint(best);
+    const unsigned int ordered = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);     // rises with the value
+    atomicMax(&g_argmax_key[r], ((unsigned long long)ordered << 32) | (0xffffffffu - (unsigned int)idx));
+    __threadfence();
+    if (atomicAdd(&g_argmax_count[r], 1u) == (unsigned int)parts - 1) {
+        __threadfence();
+        const unsigned long long key = atomicExch(&g_argmax_key[r], 0ull);
+        g_argmax_count[r] = 0;
+        const unsigned int found = 0xffffffffu - (unsigned int)(key & 0xffffffffu);
+        out[r] = found == 0x7fffffffu ? 0 : (int32_t)found;
+    }
+}
+
 }  // namespace
 
 BROLM_API int brolm_argmax(const void* logits, int rows, int vocab, void* out, cudaStream_t stream) {
     if (rows <= 0) return BROLM_OK;
     if (vocab <= 0) return BROLM_ERR_BAD_SIZE;
+    // about two blocks per SM in all, each with at least 8192 values
+    const int parts = std::min(std::min(64, 296 / rows), vocab / 8192);
+    if (parts >= 2 && rows <= ARGMAX_MAX_ROWS && (vocab & 3) == 0 && ((uintptr_t)logits & 15) == 0) {
+        argmax_parts_kernel<<<dim3(rows, parts), THREADS, 0, stream>>>((const float*)logits, vocab, (int32_t*)out);
+        return launch_status();
+    }
     argmax_kernel<<<rows, THREADS, 0, stream>>>((const float*)logits, vocab, (int32_t*)out);
     return launch_status();
 }

@@ -26,6 +26,31 @@ def test_greedy_picks_the_first_maximum():
         assert got == [plain.greedy(r) for r in x] and got[1] == 17 and got[2] == 0 and got[3] == 1000
 
 
+@pytest.mark.parametrize("n,vocab", [(1, 256000), (8, 256000), (3, 40004), (64, 65536), (200, 131072)])
+def test_greedy_over_a_large_vocabulary(n, vocab):
+    """Few rows of many values: several blocks fold a row and the last one to arrive writes the id.  Ties
+    across blocks go to the lower id, negative maxima, infinities and NaN behave as in one block, and a
+    second call finds the keys and counters at rest."""
+    x = rows(n, vocab, n + vocab)
+    x[0, vocab - 1] = x[0, 5] = 77.0                  # a tie between the first and the last block
+    if n > 1:
+        x[1] = -x[1].abs() - 1.0                      # all negative
+        x[1, vocab // 2 + 3] = -0.5
+    if n > 2:
+        x[2, 11] = float("nan")
+        x[2, vocab // 3] = float("inf")
+        x[2, vocab - 2] = float("inf")
+    sampler = bb.Sampler(bb.SamplingParams(temperature=0.0))
+    streams = torch.zeros(n, dtype=torch.int32, device=DEV)
+    want = [plain.greedy(torch.nan_to_num(r, nan=float("-inf"))) for r in x]      # a NaN is never greater: passed over
+    assert want[0] == 5 and (n <= 2 or want[2] == vocab // 3)
+    for _ in range(2):
+        assert sampler(x.to(DEV), streams, 0).tolist() == want
+    empty = torch.full((2, vocab), float("-inf"))
+    assert sampler(empty.to(DEV), streams[:2], 0).tolist() == [0, 0]
+    assert sampler(x.to(DEV), streams, 0).tolist() == want
+
+
 @pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 1.0), (0.8, 0, 1.0), (0.8, 5, 1.0), (1.3, 0, 0.7),
                                                      (0.5, 40, 0.9), (2.0, 3, 0.1), (1.0, 0, 0.0)])
 @pytest.mark.parametrize("vocab", [500, 2048, 25601])
