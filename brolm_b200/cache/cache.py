@@ -81,7 +81,10 @@ class StateGroup:
     def __init__(self, spec: StateSpec, entries: list[int], num_slots: int, dtype, device):
         self.spec = spec
         self.entries = entries
-        self.data = torch.zeros((len(entries), num_slots) + tuple(spec.shape), dtype=spec.dtype or dtype, device=device)
+        # one row more than there are slots: the padding rows of a captured decode step point there, so a
+        # mixer that indexes its state with the step's slots never touches a live sequence's state for them
+        self.data = torch.zeros((len(entries), num_slots + 1) + tuple(spec.shape), dtype=spec.dtype or dtype,
+                                device=device)
 
 
 @dataclasses.dataclass
@@ -126,6 +129,7 @@ class Cache:
             raise CacheError("max_slots must be positive")
         self.dtype, self.device = dtype, torch.device(device)
         self.slots = SlotTable(self.max_slots)
+        self.padding_slot = self.max_slots        # the slot number of padding rows: a spare row of every state group
         self.lengths = [0] * self.max_slots
         self.epochs = [0] * self.max_slots        # how often a slot has been taken: tells one tenant from the next
         self.kv_groups: list[KVGroup] = []

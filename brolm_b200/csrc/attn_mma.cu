@@ -15,13 +15,7 @@ BROLM_API int brolm_attn_prefill_mma(const void* q, int q_stride, void* out, int
     a.q = (const bf16*)q; a.out = (bf16*)out; a.q_stride = q_stride; a.out_stride = out_stride;
     a.cu_q = (const int32_t*)cu_q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.kv_stride = kv_stride;
     a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window; a.n_splits = 1;
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
-    a.sms = sms;
+    a.sms = device_sm_count();
     if (hd == 64) return launch_prefill<64, true>(a, batch, max_q_len, stream);
     if (hd == 128) return launch_prefill<128, true>(a, batch, max_q_len, stream);
     if (hd == 256) return launch_prefill<256, true>(a, batch, max_q_len, stream);

@@ -123,6 +123,17 @@ static inline int launch_status() {
     return (int)cudaGetLastError();
 }
 
+// How many SMs the current device has (asked once per process; a host that cannot say gets the B200's 148).
+static inline int device_sm_count() {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    return sms;
+}
+
 // Programmatic dependent launch.  A kernel launched through launch_pdl may begin
 // while the kernel before it in the stream is still running; it must call
 // pdl_wait() before it touches anything that kernel (or any earlier one) wrote,

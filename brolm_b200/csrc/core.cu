@@ -671,7 +671,7 @@ __global__ void softcap_kernel(const T* __restrict__ x, float* __restrict__ out,
 BROLM_API int brolm_softcap(const void* x, int dtype, void* out, long long n, float cap, cudaStream_t stream) {
     if (n <= 0) return BROLM_OK;
     long long blocks = (n + 255) / 256;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (blocks > device_sm_count() * 32) blocks = device_sm_count() * 32;
     if (dtype == BROLM_F32)
         softcap_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)x, (float*)out, (size_t)n, cap);
     else if (dtype == BROLM_BF16)

@@ -241,7 +241,7 @@ BROLM_API int brolm_argmax(const void* logits, int rows, int vocab, void* out, c
     if (rows <= 0) return BROLM_OK;
     if (vocab <= 0) return BROLM_ERR_BAD_SIZE;
     // about two blocks per SM in all, each with at least 8192 values
-    const int parts = std::min(std::min(64, 296 / rows), vocab / 8192);
+    const int parts = std::min(std::min(64, 2 * device_sm_count() / rows), vocab / 8192);
     if (parts >= 2 && rows <= ARGMAX_MAX_ROWS && (vocab & 3) == 0 && ((uintptr_t)logits & 15) == 0) {
         argmax_parts_kernel<<<dim3(rows, parts), THREADS, 0, stream>>>((const float*)logits, vocab, (int32_t*)out);
         return launch_status();

@@ -193,14 +193,6 @@ static inline int make_map_2d(CUtensorMap* map, const void* ptr, long long rows,
     return make_map_bf16(map, ptr, 2, dims, strides, box);
 }
 
-static inline int device_sms() {
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
-    return sms;
-}
+static inline int device_sms() { return device_sm_count(); }
 
 }  // namespace tc

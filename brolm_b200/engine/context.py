@@ -15,8 +15,10 @@ class StepContext:
 
     ``prefill`` steps start every sequence at position 0 with all of its
     tokens packed back to back; ``decode`` steps bring one token per sequence.
-    Rows beyond ``batch`` real sequences are padding: their position is -1 and
-    their ``kv_len`` is 0, and no kernel reads or writes the cache for them.
+    Rows beyond the real sequences are padding: their position is -1, their
+    ``kv_len`` is 0 and their slot is ``cache.padding_slot``, a spare row of
+    every state group that belongs to no sequence; no kernel reads or writes
+    keys and values for them.
     """
     mode: str                      # "prefill" | "decode"
     dtype: torch.dtype             # element type of activations and of the cache
@@ -46,5 +48,6 @@ class StepContext:
         return entry.k, entry.v, self.page_tables[entry.group_id], g.ring_tokens, g.page_size
 
     def state(self, entry: CacheEntry) -> torch.Tensor:
-        """[max_slots, *shape] state tensor of a state entry; index it with ``slots_dev``."""
+        """[max_slots + 1, *shape] state tensor of a state entry; index it with ``slots_dev``
+        (the last row is the padding rows' own)."""
         return entry.state

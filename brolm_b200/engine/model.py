@@ -8,8 +8,6 @@ final norm at the wanted rows, the output matrix and the soft-cap
 """
 from __future__ import annotations
 
-import weakref
-
 from typing import Optional
 
 import torch
@@ -17,7 +15,7 @@ import torch
 from .. import kernels
 from ..cache import Cache
 from ..config import ModelConfig, architecture_of, load_config
-from ..parts import Block, ModelLayout, Part, PartSpec, linear
+from ..parts import ModelLayout, Part, PartSpec, linear, part_class
 from ..weights import Expected, WeightsError, load_from_folder, load_from_tensors, random_tensors, write_model_folder
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -44,19 +42,17 @@ class DecoderModel:
         self.layout = layout if layout is not None else architecture_of(config.to_dict()).layout(config)
         self._shared: dict[str, Part] = {}
         self._tensor_names: list[tuple[Part, dict]] = []
-        self.blocks: list[Block] = []
+        self.blocks: list = []
         for bs in self.layout.blocks:
-            self.blocks.append(Block(
-                mixer=self._build(bs.mixer), feedforward=self._build(bs.feedforward),
-                pre_mixer_norm=self._build(bs.pre_mixer_norm), pre_ffn_norm=self._build(bs.pre_ffn_norm),
-                post_mixer_norm=self._build(bs.post_mixer_norm) if bs.post_mixer_norm else None,
-                post_ffn_norm=self._build(bs.post_ffn_norm) if bs.post_ffn_norm else None))
+            # the arrangement is a registered part too: the layout names it, nothing here knows it
+            built = {name: self._build(spec) for name, spec in bs.part_specs().items()}
+            self.blocks.append(part_class("block", bs.kind)(**built))
         self.final_norm = self._build(self.layout.final_norm)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.loaded = False
-        self._chain_plans = weakref.WeakKeyDictionary()    # cache -> compiled decode step
-        self._chain_why: Optional[str] = None              # why there is none ("": there is one)
+        self.generation = 0          # goes up whenever the tensors a captured step points at are replaced
+        self.last_hidden: Optional[torch.Tensor] = None    # the final norm's rows of the last pass
 
     # construction ---------------------------------------------------------
     def _build(self, spec: PartSpec) -> Part:
@@ -105,7 +101,9 @@ class DecoderModel:
 
     def init_random(self, seed: int = 0, weight_std: Optional[float] = None, norm_std: Optional[float] = None,
                     on_device: bool = False) -> "DecoderModel":
-        """Fill the model with seeded random weights without a folder in between."""
+        """Fill the model with seeded random weights without a folder in between: the values
+        ``write_random_model`` writes for the same seed, made on the host or (``on_device``) on the
+        model's device, which is what a model of gigabytes wants."""
         expected = self.expected_tensors()
         gen = random_tensors(expected, seed, weight_std if weight_std is not None else self.layout.weight_std,
                              norm_std if norm_std is not None else self.layout.norm_std,
@@ -126,14 +124,13 @@ class DecoderModel:
         for part, names in self._tensor_names:
             part.bind({local: tensors[ck] for local, ck in names.items() if local in part.param_specs()})
         self.loaded = True
-        self._chain_plans.clear()
-        self._chain_why = None
+        self.generation += 1
 
     # cache ----------------------------------------------------------------
     def cache_specs(self) -> list:
         specs = []
         for call in self.layout.schedule:
-            specs.append(self.blocks[call.block].mixer.cache_spec() if call.cache_of is None else None)
+            specs.append(self.blocks[call.block].cache_spec() if call.cache_of is None else None)
         return specs
 
     def new_cache(self, max_tokens: int, max_slots: Optional[int] = None, max_seq_len: Optional[int] = None) -> Cache:
@@ -145,44 +142,28 @@ class DecoderModel:
         return cache
 
     # the pass -------------------------------------------------------------
-    def _decode_chains(self, ctx):
-        """The compiled form of a decode step of few tokens (engine/fused.py), or None when the
-        step runs part by part: a prefill, more tokens than a chain takes, parts it does not know."""
-        from . import fused
-        if ctx.mode != "decode" or ctx.n_tokens > fused.ROWS or ctx.n_tokens != ctx.batch:
-            return None
-        if self._chain_why is None:
-            self._chain_why = fused.supported(self) or ""
-        if self._chain_why:
-            return None
-        key = ctx.cache
-        plan = self._chain_plans.get(key)
-        if plan is None:
-            plan = self._chain_plans[key] = fused.DecodeChains(self, ctx.cache)
-        return plan
-
     def forward(self, ctx, tokens: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """Run the packed ``tokens`` of a step; logits (len(rows), vocab), float32."""
         if not self.loaded:
             raise RuntimeError("forward: weights not loaded")
-        chains = self._decode_chains(ctx)
-        if chains is not None:
-            return chains.run(ctx, tokens, rows)
         lay = self.layout
         h = torch.empty((ctx.n_tokens, lay.embedding.hidden), dtype=torch.float32, device=self.device)
         kernels.embed_scale(tokens, self.embedding, lay.embedding.scale, h)
         sched = lay.schedule
-        x = self.blocks[sched[0].block].pre_mixer_norm.apply(h, ctx.dtype)
+        first = self.blocks[sched[0].block].entry_norm
+        x = first.apply(h, ctx.dtype) if first is not None else None
         for i, call in enumerate(sched):
             blk = self.blocks[call.block]
             src = i if call.cache_of is None else call.cache_of
             entry = ctx.cache.entries[src]
-            nxt = self.blocks[sched[i + 1].block].pre_mixer_norm if i + 1 < len(sched) else None
+            nxt = self.blocks[sched[i + 1].block].entry_norm if i + 1 < len(sched) else None
             x = blk.forward(h, x, ctx, entry, call.cache_of is None, nxt)
-        if rows.numel() == 0:
-            return torch.empty((0, lay.embedding.vocab), dtype=torch.float32, device=self.device)
         head_in = torch.float32 if self.head.dtype == torch.float32 else self.dtype
+        if rows.numel() == 0:
+            self.last_hidden = torch.empty((0, lay.embedding.hidden), dtype=head_in, device=self.device)
+            return torch.empty((0, lay.embedding.vocab), dtype=torch.float32, device=self.device)
         xf = self.final_norm.apply(h, head_in, rows=rows)
+        self.last_hidden = xf            # wlejon/brolm's hidden_out (include/brolm/gemma2.h:121-125)
         cap = float(lay.head.softcap or 0.0)
         if kernels.gemm_stream_ok(xf, self.head):
             # the largest stream of weights of a decode step: the TMA ring into tcgen05, soft-cap in the epilogue
@@ -203,11 +184,12 @@ def load_model(folder: str, dtype="bfloat16", device="cuda:0") -> DecoderModel:
 
 
 def write_random_model(config: ModelConfig, folder: str, seed: int = 0, weight_std: Optional[float] = None,
-                       norm_std: Optional[float] = None, dtype=torch.bfloat16) -> None:
-    """Random-weights mode: write config.json and model.safetensors for ``config``."""
+                       norm_std: Optional[float] = None, dtype=torch.bfloat16, device="cpu") -> None:
+    """Random-weights mode: write config.json and model.safetensors for ``config``.  The values are a
+    function of (seed, tensor name, index) alone; ``device`` only says where they are computed."""
     from .. import models  # noqa: F401
     probe = DecoderModel(config, "float32", "cpu")
     lay = probe.layout
     write_model_folder(folder, config.to_dict(), probe.expected_tensors(), seed,
                        weight_std if weight_std is not None else lay.weight_std,
-                       norm_std if norm_std is not None else lay.norm_std, dtype)
+                       norm_std if norm_std is not None else lay.norm_std, dtype, device)

@@ -88,6 +88,7 @@ class _DecodeGraph:
         # an all-padding state: the warm-up pass touches no cache
         self.hv[:] = 0
         self.hv[rows:2 * rows] = -1
+        self.hv[3 * rows:4 * rows] = cache.padding_slot
         self.hv[self.rows_off:self.pick_off] = -1
         self.dev.copy_(self.host)
         side = torch.cuda.Stream(device=dev)
@@ -109,6 +110,7 @@ class _DecodeGraph:
         try:
             with torch.cuda.graph(self.graph, pool=engine._graph_pool):
                 self.logits = engine.model.forward(self.ctx, self.tokens, self.all_rows)
+                self.hidden = engine.model.last_hidden
         finally:
             if was_enabled:
                 gc.enable()
@@ -123,6 +125,7 @@ class _DecodeGraph:
         self.copied.synchronize()              # the copy of the step before has left the pinned buffer
         hv[:4 * R] = 0
         hv[R:2 * R] = -1
+        hv[3 * R:4 * R] = cache.padding_slot
         hv[0:B] = plan.flat
         hv[R:R + B] = plan.old
         hv[2 * R:2 * R + B] = plan.new_len
@@ -168,6 +171,7 @@ class Engine:
         parts = [p for blk in model.blocks for p in blk.parts().values() if p is not None] + [model.final_norm]
         self.use_graphs = bool(use_graphs and self.device.type == "cuda" and all(p.graph_safe for p in parts))
         self._graphs: dict[tuple, _DecodeGraph] = {}
+        self._graphs_generation = model.generation
         self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
         self.last_h2d_bytes = 0          # bytes the last step copied from the host
 
@@ -181,43 +185,55 @@ class Engine:
     def close(self, slots: Sequence[int]) -> None:
         for s in slots:
             self.cache.free_slot(s)
-        if self.device.type == "cuda":
-            code = kernels.decode_chain_status(reset=True)
-            if code:
-                self.model._chain_plans.clear()      # their barrier words are not zero any more
-                raise StepError(f"close: a wait inside the decode chain ran out (code {code}); the tokens "
-                                f"decoded for these sequences are not valid")
+        # decode steps are queued without a look at the kernels' status words (that would cost a
+        # synchronisation per step); the end of a batch is where a wait that ran out is reported
+        self._check_waits("close", "the tokens decoded for these sequences are not valid")
+
+    def _check_waits(self, where: str, consequence: str) -> None:
+        """Raise if a bounded wait inside one of the tcgen05 kernels ran out since the last check.
+        Reads and resets every status word (each read waits for the device)."""
+        if self.device.type != "cuda" or self.model.dtype != torch.bfloat16:
+            return
+        codes = {"gemm_tc": kernels.gemm_tc_status(reset=True), "attn_tc": kernels.attention_tc_status(reset=True),
+                 "gemm_stream": kernels.gemm_stream_status(reset=True)}
+        bad = {k: v for k, v in codes.items() if v}
+        if bad:
+            raise StepError(f"{where}: a wait inside a tensor-core kernel ran out ({bad}), in this step or in a "
+                            f"decode step since the last check; {consequence}")
 
     # the step -------------------------------------------------------------
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
-             want: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+             want: Optional[Sequence[Sequence[int]]] = None, hidden: bool = False):
         """Run ``tokens[i]`` on ``slots[i]``; return logits [wanted, vocab] (float32, device).
 
         ``want[i]`` lists the places among ``tokens[i]`` whose logits are
         wanted (default: the last one of each), in the order given.  The
         result of a decode step is valid until the next step.
+
+        ``hidden=True`` returns ``(logits, rows)``, ``rows`` being what the
+        output matrix was given for the wanted places: the hidden state after
+        the final norm, [wanted, hidden] in the step's element type
+        (wlejon/brolm's ``hidden_out``, include/brolm/gemma2.h:121-125).
         """
         plan = self._plan(slots, tokens, want)
         if plan.mode == "decode" and self.use_graphs:
             graph = self._graph_for(plan)
             logits = graph.run(plan, self.cache)
+            rows_h = graph.hidden
             self.last_h2d_bytes = graph.host.numel() * 4
             if plan.rows != list(range(len(plan.slots))):
-                logits = logits[torch.tensor(plan.rows, dtype=torch.long, device=self.device)]
+                pick = torch.tensor(plan.rows, dtype=torch.long, device=self.device)
+                logits, rows_h = logits[pick], rows_h[pick]
             else:
-                logits = logits[:len(plan.slots)]
+                logits, rows_h = logits[:len(plan.slots)], rows_h[:len(plan.slots)]
         else:
             ctx, tok_dev, rows = self._context(plan)
             logits = self.model.forward(ctx, tok_dev, rows)
-            if plan.mode == "prefill" and self.model.dtype == torch.bfloat16 and self.device.type == "cuda":
-                # waits for the step; 0 unless a bounded wait inside a tcgen05 kernel ran out
-                code = (kernels.gemm_tc_status(reset=True) or kernels.attention_tc_status(reset=True) or
-                        kernels.gemm_stream_status(reset=True))
-                if code:
-                    raise StepError(f"step: a wait inside a tensor-core kernel ran out (code {code}); "
-                                    f"the results of this step are not valid")
+            rows_h = self.model.last_hidden
+            if plan.mode == "prefill":
+                self._check_waits("step", "the results of this step are not valid")
         self.cache.commit(dict(zip(plan.slots, plan.new_len)))
-        return logits
+        return (logits, rows_h) if hidden else logits
 
     def step_from(self, slots: Sequence[int], ids: torch.Tensor, pick: Sequence[int]) -> torch.Tensor:
         """A decode step whose tokens are still on the device: sequence ``slots[i]`` goes on with
@@ -243,6 +259,10 @@ class Engine:
         return logits
 
     def _graph_for(self, plan: _Plan) -> _DecodeGraph:
+        if self._graphs_generation != self.model.generation:
+            # the model's tensors were replaced (weights loaded again): the captured steps point at the old ones
+            self._graphs.clear()
+            self._graphs_generation = self.model.generation
         rows = _next_pow2(len(plan.slots))
         kv_cap = min(max(256, _next_pow2(max(plan.new_len))), _next_pow2(self.cache.max_positions))
         key = (rows, kv_cap)

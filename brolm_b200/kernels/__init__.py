@@ -48,6 +48,24 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+B200_SMS = 148
+_sms: dict = {}
+
+
+def device_sms(device=None) -> int:
+    """How many SMs the device of the kernels' launches has, asked once per device.  Without a CUDA
+    device (the policy functions below are plain arithmetic and are tested on the CPU) the B200's 148."""
+    if not torch.cuda.is_available():
+        return B200_SMS
+    index = torch.device(device).index if device is not None else None
+    if index is None:
+        index = torch.cuda.current_device()
+    n = _sms.get(index)
+    if n is None:
+        n = _sms[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return n
+
+
 _launches = 0
 
 
@@ -204,9 +222,10 @@ def skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
             x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def skinny_parts(x: torch.Tensor, weight: torch.Tensor, sms: int = 148) -> int:
+def skinny_parts(x: torch.Tensor, weight: torch.Tensor, sms: Optional[int] = None) -> int:
     """Into how many slices of K a few-token product is cut so that enough blocks
     stream the weights at once (about three per SM, two passes per warp at least)."""
+    sms = sms or device_sms(x.device if x.is_cuda else None)
     blocks = (weight.shape[0] + 15) // 16
     kblocks = (x.shape[1] + 63) // 64
     want = (3 * sms + blocks - 1) // blocks
@@ -233,9 +252,9 @@ def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilog
     if code == 1:
         if activation not in ACTIVATIONS:
             raise KernelError(f"skinny_gemm: unknown activation '{activation}'")
-        tiles = 4 if N >= 32 * 296 else 2
+        tiles = 4 if N >= 64 * device_sms(x.device) else 2
     else:
-        tiles = 2 if N >= 32 * 296 else 1
+        tiles = 2 if N >= 64 * device_sms(x.device) else 1
     if code == 2:
         assert out.dtype == torch.float32
     f = _fn("skinny_gemm", "brolm_skinny_gemm", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
@@ -270,17 +289,18 @@ def skinny_qkv_rope(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, po
                                                      c_void_p, c_int, c_int, c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), x.shape[0], x.shape[1],
              _ptr(positions), _ptr(cos_sin), n_q, n_kv, head_dim, _ptr(k_pages), _ptr(v_pages), _ptr(cache_rows),
-             page_size, 2 if width >= 32 * 296 else 1, _stream()), "skinny_qkv_rope")
+             page_size, 2 if width >= 64 * device_sms(x.device) else 1, _stream()), "skinny_qkv_rope")
 
 
 USE_TC_GEMM = True      # False: many-token bfloat16 products go to the library (cuBLAS) instead
 USE_PAIR_GEMM = True    # False: the tcgen05 product runs one block per tile instead of a pair of SMs per tile
 
 
-def gemm_tc_ok(x: torch.Tensor, weight: torch.Tensor, gated: bool = False, sms: int = 148) -> bool:
+def gemm_tc_ok(x: torch.Tensor, weight: torch.Tensor, gated: bool = False, sms: Optional[int] = None) -> bool:
     """Whether the tcgen05 product kernel takes these operands and has enough
     128 x 256 tiles of output to put one on every SM (fewer tiles would leave
     SMs idle while the rest stream the weights)."""
+    sms = sms or device_sms(x.device if x.is_cuda else None)
     out_cols = weight.shape[0] // 2 if gated else weight.shape[0]
     tiles = ((x.shape[0] + 127) // 128) * ((out_cols + (127 if gated else 255)) // (128 if gated else 256))
     return (USE_TC_GEMM and tiles >= sms and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and
@@ -362,8 +382,9 @@ def gemm_stream_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
             x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def gemm_stream_parts(x: torch.Tensor, weight: torch.Tensor, sms: int = 148) -> int:
+def gemm_stream_parts(x: torch.Tensor, weight: torch.Tensor, sms: Optional[int] = None) -> int:
     """Slices of K so that every SM gets a (128-row tile, slice) item of the weight stream."""
+    sms = sms or device_sms(x.device if x.is_cuda else None)
     row_tiles = (weight.shape[0] + 127) // 128
     nkb = (x.shape[1] + 63) // 64
     want = max(1, sms // row_tiles)
@@ -402,63 +423,6 @@ def gemm_stream_status(reset: bool = False) -> int:
     if not library_loaded("gemm_stream"):
         return 0                   # none of its kernels ever ran: nothing is built or loaded for the question
     f = load_library("gemm_stream").brolm_gemm_stream_status
-    f.argtypes = [c_int]
-    f.restype = c_int
-    return f(1 if reset else 0)
-
-
-# ---------------------------------------------------------------------------
-# The decode chain: lists of operations run by one persistent kernel.
-CHAIN_MAX_TOKENS = 16
-CHAIN_OP_FIELDS = 32          # eight-byte fields of an operation
-CHAIN_MAP_BYTES = 128
-# field indices of an operation, as the kernel reads them
-CHAIN_FIELDS = {n: i for i, n in enumerate(
-    ["kind", "epi", "act", "map_w", "map_x", "N", "K", "ksplit", "per", "row_tiles", "items", "ldy", "part_stride",
-     "y", "cap", "h", "parts", "n_parts", "in_stride", "hidden", "w_post", "eps_post", "off_post", "w_next",
-     "eps_next", "off_next", "out", "cos_sin", "k_pages", "v_pages", "heads", "rope"])}
-CHAIN_GEMM, CHAIN_NORM, CHAIN_ROPE = 0, 1, 2
-CHAIN_PARTS, CHAIN_GATED, CHAIN_SOFTCAP = 0, 1, 2
-
-
-def chain_make_map(t: torch.Tensor, box_rows: int) -> bytes:
-    """The TMA descriptor (128 bytes) of a row-major bfloat16 matrix, boxes of box_rows x 64."""
-    assert t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1
-    buf = ctypes.create_string_buffer(CHAIN_MAP_BYTES)
-    f = _fn("decode_chain", "brolm_chain_make_map", [c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_int])
-    global _launches
-    _check(f(ctypes.addressof(buf), _ptr(t), t.shape[0], t.shape[1], t.stride(0), box_rows), "chain_make_map")
-    _launches -= 1                 # nothing ran on the device
-    return buf.raw
-
-
-def decode_chain(maps: torch.Tensor, ops: torch.Tensor, first: int, count: int, tokens: int,
-                 positions: torch.Tensor, cache_rows: list, sync: torch.Tensor,
-                 trace: Optional[torch.Tensor] = None) -> None:
-    """Run operations [first, first + count) of a chain for ``tokens`` rows (at most CHAIN_MAX_TOKENS).
-
-    ``maps``: uint8 [n, 128] tensor maps; ``ops``: int64 [n, 32]; ``sync``: four int32 words that were
-    zero before the first launch; ``cache_rows``: up to four int32 tensors, one per key/value group;
-    ``trace``: int64 [blocks, count, 8], filled with nanosecond stamps (start, work done, barrier passed,
-    first tile multiplied, last tile issued) for looking at where a chain's time goes."""
-    assert ops.dtype == torch.int64 and ops.shape[1] == CHAIN_OP_FIELDS and ops.is_contiguous()
-    assert maps.dtype == torch.uint8 and maps.is_contiguous() and sync.dtype == torch.int32 and sync.numel() >= 4
-    assert positions.dtype == torch.int32 and positions.numel() >= tokens and len(cache_rows) <= 4
-    rows = [_ptr(r) for r in cache_rows] + [None] * (4 - len(cache_rows))
-    f = _fn("decode_chain", "brolm_decode_chain", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
-                                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
-    if trace is not None:
-        assert trace.dtype == torch.int64 and trace.is_contiguous() and trace.numel() >= 148 * count * 8
-    _check(f(_ptr(maps), _ptr(ops), first, count, tokens, _ptr(positions), rows[0], rows[1], rows[2], rows[3],
-             _ptr(sync), _ptr(trace), _stream()), "decode_chain")
-
-
-def decode_chain_status(reset: bool = False) -> int:
-    """0 if no bounded wait inside the decode chain ever ran out (or none ever ran); otherwise its code.
-    Synchronises."""
-    if not library_loaded("decode_chain"):
-        return 0
-    f = load_library("decode_chain").brolm_decode_chain_status
     f.argtypes = [c_int]
     f.restype = c_int
     return f(1 if reset else 0)
@@ -534,13 +498,14 @@ def attention_tc_status(reset: bool = False) -> int:
     return f(1 if reset else 0)
 
 
-def decode_splits(batch: int, n_kv: int, max_kv_len: int, window: int, sms: int = 148) -> int:
+def decode_splits(batch: int, n_kv: int, max_kv_len: int, window: int, sms: Optional[int] = None) -> int:
     """How many blocks share the keys of one (sequence, kv head): as many as make one wave of blocks
     over the SMs (a block holds an SM's shared memory alone), at least two pages per block and at
     most 40 splits (the last block's merge reads every split's partial result).
     Measured on a B200 at 8 kv-head pairs x 4: 4 splits (one wave) read 8192 keys in 54 us, 9 splits
     (two waves) in 58 us; one sequence with 4 kv heads and 8192 keys: 37 splits (148 blocks) 1.600 ms
     per decode step of the 2B sizes against 1.632 ms with 20 splits (80 blocks)."""
+    sms = sms or device_sms()
     keys = min(max_kv_len, window + 63) if window > 0 else max_kv_len
     tiles = max(1, (keys + 63) // 64)
     want = max(1, sms // max(1, batch * n_kv))
@@ -598,7 +563,7 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
              _ptr(streams), counter, _ptr(out), _stream()), "sample")
 
 
-__all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "embed_scale", "rmsnorm", "residual_rmsnorm",
+__all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "device_sms", "embed_scale", "rmsnorm", "residual_rmsnorm",
            "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc2", "gemm_tc2_status", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts",
-           "gemm_stream_status", "chain_make_map", "decode_chain", "decode_chain_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_tc_status", "attention_decode_mma",
+           "gemm_stream_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_tc_status", "attention_decode_mma",
            "decode_splits", "argmax", "sample"]

@@ -40,7 +40,6 @@ LIBRARIES: dict[str, list[str]] = {
     "gemm_tc2": ["gemm_tc2.cu"],
     "attn_tc": ["attn_tc.cu"],
     "gemm_stream": ["gemm_stream.cu"],
-    "decode_chain": ["decode_chain.cu"],
     "sampling": ["sampling.cu"],
 }
 HEADERS = ["common.cuh", "attn_mma.cuh", "attn_decode_noalloc.h", "tcgen05.cuh"]

@@ -3,7 +3,6 @@
     python -m brolm_b200.kernels.microbench attn_decode --batch 8 --ctx 8192 [--window 4096]
     python -m brolm_b200.kernels.microbench attn_prefill --tokens 2048
     python -m brolm_b200.kernels.microbench norms --batch 8
-    python -m brolm_b200.kernels.microbench chain --batch 8       (time stamps of the decode chain's operations)
 
 Sizes default to those of Gemma 2 2B (8 query heads, 4 kv heads of 256).  Inputs
 are larger than the L2 cache or the L2 is flushed between repetitions.
@@ -157,73 +156,9 @@ def norms(args) -> None:
     print(f"rmsnorm rows={B} hidden={H}: {ms * 1e3:.1f} us")
 
 
-def chain(args) -> None:
-    """Where the time of a decode chain goes: the operations between two attentions of a layer
-    (o, norm, gate_up, down, norm, qkv, rope), four layers with weights of their own in one launch,
-    with the kernel's nanosecond stamps of block 0 and of all blocks."""
-    from . import CHAIN_GATED, CHAIN_PARTS, decode_chain, decode_chain_status
-    from ..engine.fused import ROWS, ChainBuilder
-    from ..parts.norm import RMSNorm
-    H, inter, hd, n_q, n_kv, M = args.hidden, args.inter, args.head_dim, args.heads, args.kv_heads, args.batch
-    qd, width = n_q * hd, (n_q + 2 * n_kv) * hd
-
-    def weight(n, k):
-        return (torch.randn(n, k, device=DEV) * 0.02).to(torch.bfloat16)
-
-    def norm():
-        part = RMSNorm(H, 1e-6, 1.0)
-        part.bind({"weight": torch.zeros(H, device=DEV, dtype=torch.bfloat16)})
-        return part
-
-    b = ChainBuilder(DEV)
-    h = b.buffer("h", (ROWS, H), torch.float32)
-    x = b.buffer("x", (ROWS, H), torch.bfloat16)
-    attn = b.buffer("attn", (ROWS, qd), torch.bfloat16)
-    act = b.buffer("act", (ROWS, inter), torch.bfloat16)
-    qkv = b.buffer("qkv", (ROWS, width), torch.bfloat16)
-    table = torch.zeros(64, hd // 2, 2, device=DEV)
-    names = []
-    for _ in range(4):
-        o_parts = b.gemm(weight(H, qd), attn, "o_parts", CHAIN_PARTS)
-        b.norm(h, o_parts, norm(), norm(), x)
-        b.gemm(weight(2 * inter, H), x, act, CHAIN_GATED)
-        d_parts = b.gemm(weight(H, inter), act, "d_parts", CHAIN_PARTS)
-        b.norm(h, d_parts, norm(), norm(), x)
-        q_parts = b.gemm(weight(width, H), x, "q_parts", CHAIN_PARTS)
-        b.rope(q_parts, qkv, table, hd, n_q, n_kv, hd, None, None, 64, 0)
-        names += ["o", "norm", "gate_up", "down", "norm", "qkv", "rope"]
-    maps, ops, sync = b.finish()
-    n = len(b)
-    pos = torch.zeros(ROWS, dtype=torch.int32, device=DEV)
-    trace = torch.zeros(148, n, 8, dtype=torch.int64, device=DEV)
-    for _ in range(3):
-        decode_chain(maps, ops, 0, n, M, pos, [pos], sync)
-    decode_chain(maps, ops, 0, n, M, pos, [pos], sync, trace)
-    torch.cuda.synchronize()
-    assert decode_chain_status(reset=True) == 0
-    t = trace.cpu().double()
-    t0 = t[:, :, 0][t[:, :, 0] > 0].min()
-
-    def us(v):
-        return f"{(float(v) - float(t0)) / 1000:8.2f}" if v > 0 else "       -"
-
-    def over(o, k, fn):
-        col = t[:, o, k]
-        return fn(col[col > 0]) if bool((col > 0).any()) else 0
-
-    print(f"decode chain, {M} tokens, hidden {H}, inter {inter}: microseconds since the launch began (layers 2 and 3 of 4)")
-    print("operation | block 0: start, work done, barrier passed, first tile multiplied, last tile issued"
-          " | all blocks: last work done, last barrier passed")
-    for o in range(7, 21):
-        r = t[0, o]
-        print(f"{names[o]:9s} | {us(r[0])} {us(r[1])} {us(r[2])} {us(r[3])} {us(r[4])} | "
-              f"{us(over(o, 1, torch.max))} {us(over(o, 2, torch.max))}")
-    print(f"one layer: {(float(t[0, 14, 0]) - float(t[0, 7, 0])) / 1000:.1f} us")
-
-
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "model_prefill", "norms", "skinny", "gemm", "chain"])
+    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "model_prefill", "norms", "skinny", "gemm"])
     ap.add_argument("--inter", type=int, default=9216)
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--batch", type=int, default=8)
@@ -243,7 +178,7 @@ def main() -> None:
         from .. import kernels
         kernels.USE_TC_GEMM = False
     {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "model_prefill": model_prefill,
-     "norms": norms, "skinny": skinny, "gemm": gemm, "chain": chain}[args.what](args)
+     "norms": norms, "skinny": skinny, "gemm": gemm}[args.what](args)
 
 
 if __name__ == "__main__":

@@ -1,7 +1,8 @@
 """What every part of a layer is: a named kind, parameters with declared
 shapes, and a registry so that a layout can ask for a part by name.
 
-Kinds: ``mixer`` (attention here), ``feedforward``, ``norm``, ``position``.
+Kinds: ``mixer`` (attention here), ``feedforward``, ``norm``, ``position`` and
+``block`` (the arrangement of the others around the residual stream).
 A part gets its sizes and constants as constructor arguments and never learns
 which model it sits in; the checkpoint names of its tensors are given to it by
 the layout, per instance.
@@ -13,7 +14,7 @@ from typing import Any, Optional
 
 import torch
 
-KINDS = ("mixer", "feedforward", "norm", "position")
+KINDS = ("mixer", "feedforward", "norm", "position", "block")
 
 
 @dataclasses.dataclass(frozen=True)

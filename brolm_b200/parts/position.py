@@ -26,10 +26,15 @@ class RotaryEmbedding(Part):
         if self.rotary_dim % 2 or self.rotary_dim > head_dim:
             raise ValueError("rotary_dim must be even and at most head_dim")
         self.table: Optional[torch.Tensor] = None
+        self._outgrown: list = []      # earlier, shorter tables: a captured step may still read them
 
     def prepare(self, max_positions: int, device: torch.device) -> None:
         if self.table is not None and self.table.shape[0] >= max_positions and self.table.device == device:
             return
+        if self.table is not None:
+            # The part is shared by every layer and by every engine of its model; a CUDA graph that an
+            # earlier engine captured holds the old table's address, so the old table is never freed.
+            self._outgrown.append(self.table)
         half = self.rotary_dim // 2
         i = torch.arange(half, dtype=torch.float64)
         inv_freq = torch.tensor(self.theta, dtype=torch.float64) ** (-2.0 * i / self.rotary_dim)

@@ -9,16 +9,19 @@ import torch
 
 import brolm_b200 as bb
 
-# Two tiny configurations that differ in every size and option.
+# Tiny configurations that differ in every size and option.  A and B are the two that the benchmark
+# description states (B: multi-query, a score scale that is not head_dim ** -0.5, prompts beyond the
+# window); C is B with a vocabulary and a feed-forward width that are no multiples of 8 or of a tile.
 TINY_A = dict(vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
               num_key_value_heads=2, head_dim=16, rope_theta=10000.0, sliding_window=8,
               attn_logit_softcapping=50.0, final_logit_softcapping=30.0, query_pre_attn_scalar=16,
               rms_norm_eps=1e-6, max_position_embeddings=64)
-TINY_B = dict(vocab_size=500, hidden_size=96, intermediate_size=328, num_hidden_layers=3, num_attention_heads=6,
+TINY_B = dict(vocab_size=512, hidden_size=96, intermediate_size=320, num_hidden_layers=3, num_attention_heads=6,
               num_key_value_heads=1, head_dim=32, rope_theta=1000.0, sliding_window=16,
               attn_logit_softcapping=20.0, final_logit_softcapping=15.0, query_pre_attn_scalar=24,
               rms_norm_eps=1e-5, max_position_embeddings=128)
-TINY = {"A": (TINY_A, 0, 0.02), "B": (TINY_B, 1, 0.05)}     # name -> (config, seed, weight std)
+TINY_C = dict(TINY_B, vocab_size=500, intermediate_size=328)
+TINY = {"A": (TINY_A, 0, 0.02), "B": (TINY_B, 1, 0.05), "C": (TINY_C, 2, 0.05)}     # name -> (config, seed, weight std)
 
 
 def make_folder(tmp_path, name: str, store=torch.float32) -> str:

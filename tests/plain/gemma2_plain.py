@@ -124,6 +124,27 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, n_q: int, n_kv:
     return out.reshape(T, n_q * head_dim)
 
 
+def attention_last_query(q_row: torch.Tensor, k: torch.Tensor, v: torch.Tensor, n_q: int, n_kv: int,
+                         head_dim: int, scale: float, cap: float, window: int) -> torch.Tensor:
+    """The last row of ``attention`` alone: one query (n_q*hd,) at position T - 1 over keys 0 .. T - 1.
+
+    What a decode step computes (src/gemma2.cpp:365-367 with L = 1); the same formulas, for tests
+    whose sequences are too long for a T x T matrix per head.
+    """
+    T = k.shape[0]
+    group = n_q // n_kv
+    qh = q_row.to(DT).reshape(n_q, head_dim)
+    kh = k.to(DT).reshape(T, n_kv, head_dim)
+    vh = v.to(DT).reshape(T, n_kv, head_dim)
+    first = max(0, T - window) if window and window > 0 else 0          # 0 <= (T - 1) - j < window
+    out = torch.zeros(n_q, head_dim, dtype=DT)
+    for h in range(n_q):
+        g = h // group
+        s = soft_cap((kh[first:, g, :] @ qh[h]) * scale, cap)
+        out[h] = torch.softmax(s, dim=0) @ vh[first:, g, :]
+    return out.reshape(n_q * head_dim)
+
+
 def gelu_tanh(z: torch.Tensor) -> torch.Tensor:
     """0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))  (src/gemma2.cpp:380)."""
     return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))

@@ -60,7 +60,8 @@ def test_groups_have_storage_of_their_own():
     assert win.entries == [0, 2] and full.entries == [1] and win.ring == 128 and full.ring is None
     assert tuple(win.k.shape) == (2, 6, 2, 64, 16)          # 3 slots x 2 ring pages is all it can ever need
     assert tuple(full.k.shape) == (1, 16, 2, 64, 16)
-    assert tuple(c.state_groups[0].data.shape) == (1, 3, 3, 5)
+    assert tuple(c.state_groups[0].data.shape) == (1, 3 + 1, 3, 5)      # a spare row for a step's padding rows
+    assert c.padding_slot == 3
     assert c.entries[3] is None and c.entry(2).index == 1 and c.entry(1).k.shape[0] == 16
     with pytest.raises(CacheError):
         c.entry(3)

@@ -24,7 +24,7 @@ DEV = "cuda:0"
 TOL = {"float32": 1e-5, "bfloat16": 2e-2}
 STORE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
-CASES = [(name, dtype) for name in ("A", "B") for dtype in ("float32", "bfloat16")]
+CASES = [(name, dtype) for name in ("A", "B", "C") for dtype in ("float32", "bfloat16")]
 
 
 @pytest.fixture(scope="module")

@@ -80,6 +80,16 @@ def test_attention_mask_and_groups():
     assert not torch.allclose(plain.attention(q, k3, v, n_q, n_kv, hd, 0.3, 0.0, 3)[4], w3[4])
 
 
+def test_one_query_alone_is_the_last_row():
+    T, n_q, n_kv, hd = 23, 6, 2, 8
+    g = torch.Generator().manual_seed(7)
+    q, k, v = (torch.randn(T, n * hd, generator=g, dtype=torch.float64) for n in (n_q, n_kv, n_kv))
+    for window, cap in ((0, 0.0), (5, 3.0), (23, 0.0), (40, 1.5), (1, 0.0)):
+        whole = plain.attention(q, k, v, n_q, n_kv, hd, 0.4, cap, window)[-1]
+        assert torch.allclose(plain.attention_last_query(q[-1], k, v, n_q, n_kv, hd, 0.4, cap, window), whole,
+                              atol=1e-12)
+
+
 def test_soft_cap_and_gelu():
     x = torch.linspace(-200, 200, 101, dtype=torch.float64)
     assert float(plain.soft_cap(x, 30.0).abs().max()) <= 30.0 and torch.equal(plain.soft_cap(x, 0.0), x)
@@ -125,3 +135,39 @@ def test_sampler_oracle():
     draws = [sampling_plain.sample(logits, 1.0, 0, 1.0, u) for u in (0.0, 0.05, 0.5, 0.99)]
     cdf = torch.cumsum(probs, 0)
     assert draws == [int((cdf > u).nonzero()[0]) for u in (0.0, 0.05, 0.5, 0.99)]
+
+
+def test_two_independent_restatements_agree(tmp_path):
+    """The whole-sequence oracle (torch, masks over matrices) and the token-by-token one (NumPy, lists of
+    keys and values, complex rotation) were written apart from each other from the same lines of
+    wlejon/brolm; they must give the same logits, prompts longer than the window included.  The
+    window's edge in particular: both keep exactly ``sliding_window`` keys, the query's own included."""
+    import numpy as np
+
+    from tests.helpers import TINY, make_folder, oracle_inputs, random_prompts
+    from tests.plain import gemma2_stepwise as stepwise
+    for name in TINY:
+        folder = make_folder(tmp_path, name, torch.float32)
+        config, weights = oracle_inputs(folder)
+        W = config["sliding_window"]
+        for p in random_prompts(config["vocab_size"], [1, W, W + 1, 2 * W + 7], seed=3):
+            a = plain.forward(config, weights, p).numpy()
+            b = stepwise.forward(config, weights, p)
+            assert a.shape == b.shape
+            assert float(np.abs(a - b).max()) <= 1e-9 * max(1.0, float(np.abs(a).max())), (name, len(p))
+    # the edge itself: with window W the logits at position W do not depend on token 0, at W - 1 they do
+    config, weights = oracle_inputs(make_folder(tmp_path, "A", torch.float32))
+    config = {**config, "layer_types": ["sliding_attention"] * config["num_hidden_layers"]}
+    W = config["sliding_window"]
+    p = random_prompts(config["vocab_size"], [W + 1], seed=4)[0]
+    q = [(p[0] + 1) % config["vocab_size"]] + p[1:]
+    for impl in (lambda ids: plain.forward(config, weights, ids).numpy(), lambda ids: stepwise.forward(config, weights, ids)):
+        x, y = impl(p), impl(q)
+        # every layer slides: position W sees keys 1..W only, and those keys were made from positions that
+        # themselves saw token 0 at most through W - 1 earlier keys ... in a model of one layer; with more
+        # layers token 0 reaches further, so the statement is checked on the first layer's reach only
+        assert float(np.abs(x[W - 1] - y[W - 1]).max()) > 1e-6
+    one = {**config, "num_hidden_layers": 1, "layer_types": ["sliding_attention"]}
+    for impl in (lambda ids: plain.forward(one, weights, ids).numpy(), lambda ids: stepwise.forward(one, weights, ids)):
+        x, y = impl(p), impl(q)
+        assert float(np.abs(x[W] - y[W]).max()) == 0.0 and float(np.abs(x[W - 1] - y[W - 1]).max()) > 1e-6

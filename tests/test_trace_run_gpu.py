@@ -31,7 +31,7 @@ def read(out, step, vocab):
     return torch.from_numpy(np.fromfile(os.path.join(out, f"{step}.f32"), dtype="<f4").reshape(-1, vocab).copy())
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_three_ways(tmp_path, name, dtype):
     folder = make_folder(tmp_path, name, STORE[dtype])

@@ -47,6 +47,44 @@ def test_random_folder_is_reproducible_and_seeded(tmp_path):
     assert json.load(open(tmp_path / "s0" / "config.json"))["architectures"] == ["Gemma2ForCausalLM"]
 
 
+def test_random_values_are_a_function_of_seed_name_and_index():
+    """The generator restated with Python's own integers: splitmix64 at 3 i + j + 1 steps from the key,
+    twelve 16-bit fields summed, centred and scaled (brolm_b200/weights/random_init.py)."""
+    import hashlib
+
+    import numpy as np
+
+    from brolm_b200.weights.random_init import random_tensor
+    M = (1 << 64) - 1
+
+    def mix(z):
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M
+        return z ^ (z >> 31)
+
+    name, seed, std = "model.layers.3.mlp.up_proj.weight", 5, 0.02
+    key = int.from_bytes(hashlib.sha256(f"{seed}:{name}".encode()).digest()[:8], "little")
+    got = random_tensor(seed, name, (7, 9), std, torch.float32, "cpu").reshape(-1)
+    for i in (0, 1, 8, 62):
+        total = 0
+        for j in range(3):
+            z = mix((key + (3 * i + j + 1) * 0x9E3779B97F4A7C15) & M)
+            total += sum((z >> s) & 0xFFFF for s in (0, 16, 32, 48))
+        want = np.float32(np.float32(total - 393210) / np.float32(65536.0)) * np.float32(std)
+        assert float(got[i]) == float(want)
+    # a tensor does not depend on how it is cut into chunks, and looks normal
+    from brolm_b200.weights import random_init
+    big = random_tensor(1, "t", (1000, 300), 1.0, torch.float32, "cpu")
+    old = random_init.CHUNK
+    random_init.CHUNK = 4099
+    try:
+        assert torch.equal(random_tensor(1, "t", (1000, 300), 1.0, torch.float32, "cpu"), big)
+    finally:
+        random_init.CHUNK = old
+    assert abs(float(big.mean())) < 0.01 and abs(float(big.std()) - 1.0) < 0.01 and float(big.abs().max()) < 6.0
+    assert 0.66 < float((big.abs() < 1.0).float().mean()) < 0.70
+
+
 def test_kept_element_types(tmp_path):
     folder = make_folder(tmp_path, "A", torch.bfloat16)
     f = SafetensorsFile(os.path.join(folder, "model.safetensors"))
