@@ -26,6 +26,14 @@
 //   on the GPU (different streams, or a second call issued before the first
 //   has finished on another stream) race on the array; keep calls on one
 //   stream or order them yourself.
+// * The splits of a (sequence, kv head) are merged by whichever of their
+//   blocks finishes last; the blocks count themselves on a second file-scope
+//   __device__ array of ticket words (g_decode_tickets in attn_mma.cuh, one
+//   copy per loaded library).  Those words are shared between calls in the
+//   same way as the scratch, and by the ordinary entry point
+//   brolm_attn_decode_mma as well: two launches of either kind that overlap
+//   on the GPU would count on the same words.  The same rule covers both:
+//   one stream, or your own ordering.
 // * The function calls no cudaMalloc, cudaFree or any allocating routine.
 //
 // Arguments and result are those of brolm_attn_decode_mma (attn_mma.cu)

@@ -122,6 +122,32 @@ def skinny(args) -> None:
         print(f"skinny {name} rows={B} N={w.shape[0]} K={k}: {ms * 1e3:.1f} us, {w.numel() * 2 / ms / 1e6:.0f} GB/s of weights")
 
 
+def stream(args) -> None:
+    """The products of one layer at --batch tokens (17 to 128): the tcgen05 weight stream against the library."""
+    from . import gemm_stream, gemm_stream_parts, gemm_stream_status
+    B, H, F = args.batch, args.hidden, args.inter
+    qkv = (args.heads + 2 * args.kv_heads) * args.head_dim
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    total_own = total_lib = 0.0
+    for name, n, k, epi in (("qkv", qkv, H, "store"), ("o", H, args.heads * args.head_dim, "parts"),
+                            ("gate_up+act", F, H, "gated"), ("down", H, F, "parts")):
+        x = torch.randn(B, k, device=DEV).to(torch.bfloat16)
+        rows = 2 * n if epi == "gated" else n
+        w = torch.randn(rows, k, device=DEV).to(torch.bfloat16)
+        parts = gemm_stream_parts(x, w) if epi == "parts" else 1
+        out = (torch.empty(parts, B, n, dtype=torch.float32, device=DEV) if parts > 1 else
+               torch.empty(B, n, dtype=torch.float32 if epi == "parts" else torch.bfloat16, device=DEV))
+        wide = torch.empty(B, rows, dtype=torch.bfloat16, device=DEV)
+        own = timed(lambda: gemm_stream(x, w, out, "gated" if epi == "gated" else "store"), args.reps, flush)
+        lib = timed(lambda: torch.mm(x, w.t(), out=wide), args.reps, flush)
+        total_own += own
+        total_lib += lib
+        print(f"gemm_stream {name} rows={B} N={rows} K={k} slices={parts}: {own * 1e3:.1f} us, "
+              f"{w.numel() * 2 / own / 1e6:.0f} GB/s of weights (library product alone: {lib * 1e3:.1f} us, "
+              f"{w.numel() * 2 / lib / 1e6:.0f} GB/s)")
+    print(f"one layer: {total_own * 1e3:.1f} us own, {total_lib * 1e3:.1f} us library; status {gemm_stream_status()}")
+
+
 def gemm(args) -> None:
     """The many-token products of one Gemma 2 2B layer at --tokens tokens on tcgen05, against the library."""
     T, H, F = args.tokens, args.hidden, args.inter
@@ -158,7 +184,7 @@ def norms(args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "model_prefill", "norms", "skinny", "gemm"])
+    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "model_prefill", "norms", "skinny", "gemm", "stream"])
     ap.add_argument("--inter", type=int, default=9216)
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--batch", type=int, default=8)
@@ -178,7 +204,7 @@ def main() -> None:
         from .. import kernels
         kernels.USE_TC_GEMM = False
     {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "model_prefill": model_prefill,
-     "norms": norms, "skinny": skinny, "gemm": gemm}[args.what](args)
+     "norms": norms, "skinny": skinny, "gemm": gemm, "stream": stream}[args.what](args)
 
 
 if __name__ == "__main__":

@@ -179,13 +179,19 @@ def decoder_layer(h: torch.Tensor, w: dict, prefix: str, config: dict, layer: in
     return h + rms_norm(y, w[prefix + "post_feedforward_layernorm.weight"], eps)
 
 
-def forward(config: dict, w: dict, ids) -> torch.Tensor:
-    """Logits (T, vocab) of one whole sequence (src/gemma2.cpp:272-288, 326-415)."""
+def hidden(config: dict, w: dict, ids) -> torch.Tensor:
+    """The rows the output matrix is given, (T, hidden): the residual stream after the final norm,
+    what the reference hands out as ``hidden_out`` (src/gemma2.cpp:389-391)."""
     ids = torch.as_tensor(ids)
     h = embed(w["model.embed_tokens.weight"], ids, config["hidden_size"])
     for i in range(config["num_hidden_layers"]):
         h = decoder_layer(h, w, f"model.layers.{i}.", config, i)
-    x = rms_norm(h, w["model.norm.weight"], config["rms_norm_eps"])
+    return rms_norm(h, w["model.norm.weight"], config["rms_norm_eps"])
+
+
+def forward(config: dict, w: dict, ids) -> torch.Tensor:
+    """Logits (T, vocab) of one whole sequence (src/gemma2.cpp:272-288, 326-415)."""
+    x = hidden(config, w, ids)
     head = w.get("lm_head.weight", w["model.embed_tokens.weight"])  # src/gemma2.cpp:223-234
     return soft_cap(linear(x, head), config.get("final_logit_softcapping") or 0.0)
 

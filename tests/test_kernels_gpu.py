@@ -419,6 +419,32 @@ def test_attention_tc_scores_beyond_the_cap(n_q, n_kv, hd, window, cap, gain):
         t += n
 
 
+@pytest.mark.parametrize("n_q,n_kv,hd,window,cap,lengths", [(8, 4, 256, 512, 50.0, [1500, 130]),
+                                                            (8, 4, 256, 0, 50.0, [2100]),
+                                                            (4, 2, 128, 0, 30.0, [2100, 700])])
+def test_attention_tc_long_prompts(n_q, n_kv, hd, window, cap, lengths):
+    """Prompts of many key tiles: 1,500 tokens with a window of 512 (row blocks whose first key tile is
+    not tile 0, windows that cut tiles at both ends) and 2,100 tokens without a window."""
+    g = torch.Generator().manual_seed(11)
+    T = sum(lengths)
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * hd, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(hd)
+    dq = qkv.to(DEV)
+    out = torch.empty(T, n_q * hd, dtype=torch.bfloat16, device=DEV)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=DEV)
+    kernels.attention_prefill_tc(dq[:, :n_q * hd], out, cu, dq[:, n_q * hd:(n_q + n_kv) * hd], dq[:, (n_q + n_kv) * hd:],
+                                 n_kv=n_kv, group=n_q // n_kv, head_dim=hd, scale=scale, cap=cap, window=window,
+                                 batch=len(lengths), max_q_len=max(lengths))
+    assert kernels.attention_tc_status() == 0
+    t = 0
+    for n in lengths:
+        s = qkv[t:t + n]
+        ref = _attention_oracle(s[:, :n_q * hd], s[:, n_q * hd:(n_q + n_kv) * hd], s[:, (n_q + n_kv) * hd:],
+                                n_q, n_kv, hd, scale, cap, window)
+        close(out[t:t + n], ref, torch.bfloat16, scale=float(ref.abs().max()))
+        t += n
+
+
 def _paged_case(dtype, n_q, n_kv, hd, window, cap, lengths, page=64, special=None, seed=0, kernel="simt", splits=1):
     """Decode pass: one query per sequence over a scattered, possibly ring-shaped cache."""
     g = torch.Generator().manual_seed(seed)
@@ -456,10 +482,14 @@ def _paged_case(dtype, n_q, n_kv, hd, window, cap, lengths, page=64, special=Non
                                page_table=pt.to(DEV), ring=ring, page_size=page, **kw)
     assert bool(torch.isfinite(out.float()).all()), "a place of the cache that was never written was read"
     for b, n in enumerate(lengths):
-        # oracle over the whole sequence with the query as the last row
-        qfull = torch.zeros(n, n_q * hd).to(dtype)
-        qfull[-1] = qs[b][0]
-        ref = _attention_oracle(qfull, ks[b], vs[b], n_q, n_kv, hd, scale, cap, window)[-1]
+        if n > 1200:
+            # too long for a matrix per head: the oracle's form for one query (the plain tests tie it to the other)
+            ref = plain.attention_last_query(qs[b][0], ks[b], vs[b], n_q, n_kv, hd, scale, cap, window)
+        else:
+            # oracle over the whole sequence with the query as the last row
+            qfull = torch.zeros(n, n_q * hd).to(dtype)
+            qfull[-1] = qs[b][0]
+            ref = _attention_oracle(qfull, ks[b], vs[b], n_q, n_kv, hd, scale, cap, window)[-1]
         close(out[b], ref, dtype, scale=float(ref.abs().max()))
 
 
@@ -477,6 +507,36 @@ def test_attention_paged(dtype, n_q, n_kv, hd, window, cap):
 def test_attention_decode_tensor_cores(splits, n_q, n_kv, hd, window, cap):
     _paged_case(torch.bfloat16, n_q, n_kv, hd, window, cap, lengths=[1, 63, 64, 65, 129, 300, 1000],
                 seed=hd + window, kernel="mma", splits=splits)
+
+
+@pytest.mark.parametrize("splits", [17, 33, 40])
+@pytest.mark.parametrize("n_q,n_kv,hd,window,cap", [(8, 4, 256, 0, 50.0), (8, 4, 256, 4096, 50.0), (32, 16, 128, 0, 50.0),
+                                                    (6, 1, 32, 0, 20.0)])
+def test_attention_decode_many_splits(splits, n_q, n_kv, hd, window, cap):
+    """More splits than a warp has lanes (the merge then takes two rounds per thread), as one sequence of
+    8,192 keys on four kv heads gets them (37 on 148 SMs); sequences of a few keys beside long ones leave
+    most splits empty; with the real window the ring of 64 pages is read through 65 tiles."""
+    _paged_case(torch.bfloat16, n_q, n_kv, hd, window, cap, lengths=[5300, 70, 2600, 4161], seed=hd + splits,
+                kernel="mma", splits=splits)
+
+
+def test_attention_decode_far_key_at_the_splits_of_one_long_sequence():
+    """One sequence of 8,192 keys: the launch policy gives it 37 splits.  Key 17 carries all the weight."""
+    n_q, n_kv, hd = 8, 4, 64
+    splits = kernels.decode_splits(1, n_kv, 8192, 0, sms=148)
+    assert splits == 37
+
+    def special(qs, ks, vs):
+        ks[0][17] = 0
+        qs[0][:] = 0
+        for g in range(n_kv):
+            ks[0][17, g * hd] = 8.0
+        for h in range(n_q):
+            qs[0][0, h * hd] = 8.0
+        vs[0][17] = 5.0
+
+    _paged_case(torch.bfloat16, n_q, n_kv, hd, 0, 0.0, lengths=[8192], special=special, seed=3, kernel="mma",
+                splits=splits)
 
 
 def test_attention_decode_tensor_cores_skips_padding_rows():

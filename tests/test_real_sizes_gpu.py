@@ -1,7 +1,9 @@
 """The layer sizes of the published Gemma 2 models (2B, 9B, 27B) with two layers
 and a small vocabulary: the kernels must take these widths, head counts and
-head sizes, and the engine must still match the plain implementation, in
-bfloat16, for a prompt pass and for decode steps in a batch."""
+head sizes, and the engine must still match the plain implementation for a
+prompt pass and for decode steps in a batch: in bfloat16 for all three, and in
+true 32-bit for the 2B sizes (the CUDA-core product at K = 9,216 and the exact
+attention at heads of 256)."""
 import pytest
 import torch
 
@@ -22,13 +24,15 @@ SIZES = {
 }
 
 
-@pytest.mark.parametrize("name", list(SIZES))
-def test_layer_sizes_of_the_published_models(tmp_path, name):
+@pytest.mark.parametrize("name,dtype,tol", [("2b", "bfloat16", 2e-2), ("9b", "bfloat16", 2e-2), ("27b", "bfloat16", 2e-2),
+                                            ("2b", "float32", 1e-5)])
+def test_layer_sizes_of_the_published_models(tmp_path, name, dtype, tol):
     cfg = bb.Gemma2Config(vocab_size=1000, num_hidden_layers=2, **SIZES[name])
     folder = str(tmp_path / name)
-    bb.write_random_model(cfg, folder, seed=2, dtype=torch.bfloat16)
+    # made on the device (seconds instead of minutes for 27B's 1.1 G values); the file is the same
+    bb.write_random_model(cfg, folder, seed=2, dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32, device=DEV)
     config, weights = oracle_inputs(folder)
-    model = bb.load_model(folder, dtype="bfloat16", device=DEV)
+    model = bb.load_model(folder, dtype=dtype, device=DEV)
     eng = bb.Engine(model, max_tokens=1024, max_slots=3)
     prompts = random_prompts(1000, [70, 9, 33], seed=3)
     refs = [plain.forward(config, weights, p) for p in prompts]
@@ -45,4 +49,4 @@ def test_layer_sizes_of_the_published_models(tmp_path, name):
         for i, (r, k) in enumerate(zip(refs, pre)):
             worst = max(worst, float((got[i].double().cpu() - r[k + step]).abs().max()) / float(r[k + step].abs().max()))
     eng.close(slots)
-    assert worst <= 2e-2, f"relative error {worst:.3e}"
+    assert worst <= tol, f"relative error {worst:.3e}"

@@ -6,7 +6,9 @@ calls).  For them ``brolm_attn_decode_mma_noalloc`` keeps the scratch of the
 split-KV merge in a fixed array inside the library.  This test loads the
 library with ctypes, calls the symbol itself (no Python wrapper in between)
 twice in a row with different shapes, and checks each result against the
-ordinary entry point, which takes its scratch from the caller.  The second
+ordinary entry point, which takes its scratch from the caller, and against
+the plain float64 attention (a fault that both entry points share would
+pass the first comparison).  The second
 call is smaller than the first, so anything stale in the shared array would
 show.  It also checks that a call beyond the array's size is refused.
 
@@ -22,6 +24,7 @@ import torch
 
 from brolm_b200 import kernels
 from brolm_b200.kernels.build import load_library
+from tests.plain import gemma2_plain as plain
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -71,6 +74,20 @@ def run_both(f, c, splits):
     torch.cuda.synchronize()
     err = float((got.float() - want.float()).abs().max()) / float(want.float().abs().max())
     assert err <= TOL, f"relative error {err:.3e}"
+    # and against the plain attention: each sequence's keys and values gathered back from its pages
+    kp, vp, table = c["kp"].cpu(), c["vp"].cpu(), c["table"].cpu()
+    n_q = c["n_kv"] * c["group"]
+    for b, n in enumerate(c["kv_len"].tolist()):
+        first = max(0, n - c["window"]) if c["window"] else 0
+        k = torch.zeros(n, c["n_kv"] * c["hd"])
+        v = torch.zeros(n, c["n_kv"] * c["hd"])
+        for p in range(first, n):
+            r = p % c["ring"]
+            k[p] = kp[int(table[b, r // 64]), :, r % 64, :].reshape(-1).float()
+            v[p] = vp[int(table[b, r // 64]), :, r % 64, :].reshape(-1).float()
+        ref = plain.attention_last_query(c["q"][b].cpu().float(), k, v, n_q, c["n_kv"], c["hd"], scale, cap, c["window"])
+        err = float((got[b].cpu().double() - ref).abs().max()) / float(ref.abs().max())
+        assert err <= TOL, f"sequence {b}: relative error {err:.3e} against the plain attention"
 
 
 def test_two_calls_in_a_row_match_the_ordinary_entry_point():
