@@ -68,6 +68,10 @@ using namespace tc;
 __device__ __forceinline__ bool wait_on(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
     return mbar_wait(bar, parity, give_up, &g_attn_tc_error, code);
 }
+// after the block gave up: loads in flight are waited for under the second flag
+__device__ __forceinline__ bool drain_on(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
+    return mbar_wait(bar, parity, give_up, &g_attn_tc_error, code, true);
+}
 __device__ __forceinline__ uint32_t idesc(int m, int n, int b_mn_major) { return idesc_bf16(m, n, b_mn_major); }
 
 // The shapes that depend on the head size.  A key tile is KU units (parts of the head size, all 128 keys), a
@@ -139,6 +143,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
         }
         give_up[0] = 0;
         give_up[1] = 0;
+        give_up[2] = tc::g_stall_code;
         mbar_init_fence();
     }
     if (warp == 1) {
@@ -190,8 +195,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
                 if (ok) load_v(j);
             }
             if (*give_up) {        // let the loads in flight land before the block goes away
-                wait_on(bar(Q_FULL), 0, give_up + 1, 9);
-                for (int i = max(0, u - SLOTS); i < u; ++i) wait_on(bar(U_FULL + i % SLOTS), (i / SLOTS) & 1, give_up + 1, 9);
+                drain_on(bar(Q_FULL), 0, give_up, 9);
+                for (int i = max(0, u - SLOTS); i < u; ++i) drain_on(bar(U_FULL + i % SLOTS), (i / SLOTS) & 1, give_up, 9);
             }
         }
     } else if (warp == 1) {
@@ -453,3 +458,5 @@ BROLM_API int brolm_attn_tc_status(int reset) {
     }
     return v;
 }
+
+BROLM_WAIT_CONTROL(attn_tc)

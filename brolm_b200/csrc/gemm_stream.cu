@@ -57,6 +57,10 @@ struct StreamArgs {
 __device__ __forceinline__ bool wait_on(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
     return mbar_wait(bar, parity, give_up, &g_gemm_stream_error, code);
 }
+// after the block gave up: loads in flight are waited for under the second flag
+__device__ __forceinline__ bool drain_on(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
+    return mbar_wait(bar, parity, give_up, &g_gemm_stream_error, code, true);
+}
 
 template <int BT, int EPI>
 struct Shape {
@@ -106,6 +110,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(const __grid_co
         }
         give_up[0] = 0;
         give_up[1] = 0;
+        give_up[2] = tc::g_stall_code;
         mbar_init_fence();
     }
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), S::TMEM_COLS);
@@ -163,7 +168,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(const __grid_co
             pdl_trigger();                                   // the stream is issued: the next kernel may move in
             if (*give_up) {
                 for (int j = max(0, it - STAGES); j < it; ++j)
-                    wait_on(full0 + 8 * (j % STAGES), (j / STAGES) & 1, give_up + 1, 4);
+                    drain_on(full0 + 8 * (j % STAGES), (j / STAGES) & 1, give_up, 4);
             }
         }
     } else if (warp == 1) {
@@ -323,3 +328,5 @@ BROLM_API int brolm_gemm_stream_status(int reset) {
     }
     return v;
 }
+
+BROLM_WAIT_CONTROL(gemm_stream)

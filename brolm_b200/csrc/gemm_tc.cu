@@ -58,6 +58,10 @@ __device__ __forceinline__ float act_apply(float z, int act) { return fast_gate_
 __device__ __forceinline__ bool wait_on(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
     return mbar_wait(bar, parity, give_up, &g_gemm_tc_error, code);
 }
+// after the block gave up: loads in flight are waited for under the second flag
+__device__ __forceinline__ bool drain_on(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
+    return mbar_wait(bar, parity, give_up, &g_gemm_tc_error, code, true);
+}
 
 template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
@@ -88,6 +92,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
         }
         give_up[0] = 0;
         give_up[1] = 0;      // the flag of the drain waits below
+        give_up[2] = tc::g_stall_code;
         mbar_init_fence();
     }
     if (warp == 1) {
@@ -122,7 +127,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
             if (*give_up) {
                 // let the loads that are still in flight land before the block goes away
                 for (int j = max(0, it - STAGES); j < it; ++j)
-                    wait_on(full0 + 8 * (j % STAGES), (j / STAGES) & 1, give_up + 1, 4);
+                    drain_on(full0 + 8 * (j % STAGES), (j / STAGES) & 1, give_up, 4);
             }
         }
     } else if (warp == 1) {
@@ -274,3 +279,5 @@ BROLM_API int brolm_gemm_tc_status(int reset) {
     }
     return v;
 }
+
+BROLM_WAIT_CONTROL(gemm_tc)

@@ -44,6 +44,10 @@ using namespace tc;
 __device__ __forceinline__ bool wait_on(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
     return mbar_wait(bar, parity, give_up, &g_gemm_tc2_error, code);
 }
+// after the block gave up: loads in flight are waited for under the second flag
+__device__ __forceinline__ bool drain_on(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
+    return mbar_wait(bar, parity, give_up, &g_gemm_tc2_error, code, true);
+}
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -110,6 +114,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
         give_up[0] = aligned ? 0 : 1;
         give_up[1] = 0;
+        give_up[2] = tc::g_stall_code;
         if (!aligned) atomicCAS(&g_gemm_tc2_error, 0, 13);
         mbar_init_fence();
     }
@@ -139,7 +144,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
             if (*give_up && rank == 0) {
                 for (int j = max(0, it - STAGES); j < it; ++j)
-                    wait_on(full0 + 8 * (j % STAGES), (j / STAGES) & 1, give_up + 1, 4);
+                    drain_on(full0 + 8 * (j % STAGES), (j / STAGES) & 1, give_up, 4);
             }
         }
     } else if (warp == 1) {
@@ -280,3 +285,5 @@ BROLM_API int brolm_gemm_tc2_status(int reset) {
     }
     return v;
 }
+
+BROLM_WAIT_CONTROL(gemm_tc2)

@@ -3,11 +3,19 @@
 // tcgen05.mma, tensor-memory loads and stores, and the host-side tensor-map encoder.
 //
 // Bounded waits.  No wait in these kernels can spin for ever: mbar_wait gives up
-// after WAIT_CYCLES clock cycles (about a second), raises the block's give-up flag
-// that every other waiting role polls, and records a code in the kernel file's
-// error word.  The kernel then lets its outstanding loads land, frees its tensor
-// memory and returns; the launch's results are not valid and the host learns of
-// it through the file's status function.
+// after g_wait_cycles clock cycles (about a second unless the host sets another
+// limit), raises the block's give-up flag that every other waiting role polls,
+// and records a code in the kernel file's error word.  The kernel then lets its
+// outstanding loads land, frees its tensor memory and returns; the launch's
+// results are not valid and the host learns of it through the file's status
+// function.
+//
+// That path can be exercised without a fault: every library built from this
+// header exports brolm_<library>_wait_control(cycles, stall_code).  `cycles`
+// sets the limit (<= 0: the default); a non-zero `stall_code` makes the waits
+// that carry this code behave as if their barrier never completed, so they run
+// into the limit and the kernel gives up as it would for a load that never
+// arrived.  Nothing hangs and nothing traps; the context stays usable.
 #pragma once
 
 #include "common.cuh"
@@ -17,6 +25,20 @@
 namespace tc {
 
 constexpr long long WAIT_CYCLES = 2000000000ll;
+__device__ long long g_wait_cycles = WAIT_CYCLES;     // one copy per library: this header is its only definition
+__device__ int g_stall_code = 0;                      // tests only: waits with this code never see their barrier
+                                                      // (a kernel copies it to give_up[2] when it starts)
+
+static inline int set_wait_control(long long cycles, int stall_code) {
+    const long long c = cycles > 0 ? cycles : WAIT_CYCLES;
+    cudaError_t e = cudaMemcpyToSymbol(g_wait_cycles, &c, sizeof(c));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_stall_code, &stall_code, sizeof(stall_code));
+    return (int)e;
+}
+#define BROLM_WAIT_CONTROL(library)                                                        \
+    BROLM_API int brolm_##library##_wait_control(long long cycles, int stall_code) {       \
+        return tc::set_wait_control(cycles, stall_code);                                   \
+    }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -39,14 +61,20 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Returns false when it gave up: its own limit ran out (then *error gets `code`, if it was 0) or
-// another role of the block had already given up.
-__device__ inline bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int* error, int code) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
+// another role of the block had already given up.  give_up: three ints in shared memory that the
+// kernel sets when it starts: [0] the block's give-up flag, [1] that of the drain waits, [2] g_stall_code.
+// `flags`: the three ints; `drain`: one of the waits that let loads in flight land after the block gave up
+// (they watch flags[1] and are never stalled).
+__device__ inline bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* flags, int* error, int code,
+                                 bool drain = false) {
+    volatile int* give_up = flags + (drain ? 1 : 0);
+    const bool stalled = !drain && flags[2] == code;          // (0 in every ordinary launch)
+    if (!stalled && mbar_try(bar, parity)) return true;       // (try_wait itself may hold the thread for a while)
+    const long long t0 = clock64(), limit = g_wait_cycles;
     while (true) {
-        if (mbar_try(bar, parity)) return true;
+        if (!stalled && mbar_try(bar, parity)) return true;
         if (*give_up) return false;
-        if (clock64() - t0 > WAIT_CYCLES) {
+        if (clock64() - t0 > limit) {
             *give_up = 1;
             atomicCAS(error, 0, code);
             return false;

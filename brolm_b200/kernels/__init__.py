@@ -371,6 +371,24 @@ def gemm_tc_status(reset: bool = False) -> int:
     return f(1 if reset else 0)
 
 
+WAIT_LIBRARIES = ("gemm_tc", "gemm_tc2", "gemm_stream", "attn_tc")
+
+
+def wait_control(library: str, cycles: int = 0, stall_code: int = 0) -> None:
+    """The limit of the bounded waits inside one of the tcgen05 libraries, in clock cycles (0: the default of
+    about a second), and, for tests of the give-up path, the code of the waits that shall behave as if
+    their barrier never completed (0: none).  A wait that runs out ends its kernel early; the library's
+    status function then reports the code and ``Engine.step`` raises ``StepError``."""
+    if library not in WAIT_LIBRARIES:
+        raise KernelError(f"wait_control: '{library}' has no bounded waits (libraries: {WAIT_LIBRARIES})")
+    f = getattr(load_library(library), f"brolm_{library}_wait_control")
+    f.argtypes = [c_longlong, c_int]
+    f.restype = c_int
+    status = f(int(cycles), int(stall_code))
+    if status:
+        raise KernelError(f"wait_control: CUDA error {status}")
+
+
 STREAM_MAX_ROWS = 128
 
 
@@ -563,7 +581,7 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
              _ptr(streams), counter, _ptr(out), _stream()), "sample")
 
 
-__all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "device_sms", "embed_scale", "rmsnorm", "residual_rmsnorm",
+__all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "device_sms", "wait_control", "embed_scale", "rmsnorm", "residual_rmsnorm",
            "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc2", "gemm_tc2_status", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts",
            "gemm_stream_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_tc_status", "attention_decode_mma",
            "decode_splits", "argmax", "sample"]
