@@ -560,6 +560,95 @@ __global__ void __launch_bounds__(256) rope_kv_write_vec_kernel(bf16* __restrict
     }
 }
 
+// The same for a q/k/v projection that arrives as float partial sums of K slices (the few-token tcgen05
+// product cut along K so that every SM streams weights): the slices are added in order, q and k rotated,
+// and everything rounded to bfloat16 once, into the packed q/k/v row and into the cache pages.
+// rot == hd (or no rotation), hd a multiple of 16; one block per token, eight pairs per thread and item.
+__global__ void __launch_bounds__(256) rope_kv_write_parts_kernel(const float* __restrict__ parts, int n_parts,
+                                                                  long long part_stride, bf16* __restrict__ qkv,
+                                                                  int ld_out, const int32_t* __restrict__ positions,
+                                                                  const float2* __restrict__ cos_sin, int n_q,
+                                                                  int n_kv, int hd, bf16* __restrict__ k_pages,
+                                                                  bf16* __restrict__ v_pages,
+                                                                  const int32_t* __restrict__ cache_rows,
+                                                                  int page_size) {
+    const int t = blockIdx.x;
+    const int pos = positions[t];                 // (the host's, written before the step's first kernel)
+    const int crow = (k_pages && pos >= 0) ? cache_rows[t] : -1;
+    pdl_trigger();
+    pdl_wait();
+    if (pos < 0) return;
+    const int half = hd >> 1, per_head = half >> 3;
+    const int heads = n_q + 2 * n_kv, width = heads * hd;
+    const float* src = parts + (size_t)t * width;
+    bf16* row = qkv + (size_t)t * ld_out;
+    for (int item = threadIdx.x; item < heads * per_head; item += blockDim.x) {
+        const int head = item / per_head, i0 = (item - head * per_head) << 3;
+        const bool is_v = head >= n_q + n_kv, is_k = !is_v && head >= n_q;
+        const bool rotate = !is_v && cos_sin != nullptr;
+        float a[8], b[8];
+        load8(src + (size_t)head * hd + i0, a);
+        load8(src + (size_t)head * hd + half + i0, b);
+        for (int s = 1; s < n_parts; ++s) {                    // added in the order of the slices
+            float ta[8], tb[8];
+            load8(src + (size_t)s * part_stride + (size_t)head * hd + i0, ta);
+            load8(src + (size_t)s * part_stride + (size_t)head * hd + half + i0, tb);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { a[j] += ta[j]; b[j] += tb[j]; }
+        }
+        if (rotate) {
+            const float4* cs = reinterpret_cast<const float4*>(cos_sin + (size_t)pos * half + i0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 c = cs[j];                       // (cos, sin) of pairs 2j and 2j + 1
+                const float a0 = a[2 * j], a1 = a[2 * j + 1], b0 = b[2 * j], b1 = b[2 * j + 1];
+                a[2 * j] = a0 * c.x - b0 * c.y;
+                b[2 * j] = a0 * c.y + b0 * c.x;
+                a[2 * j + 1] = a1 * c.z - b1 * c.w;
+                b[2 * j + 1] = a1 * c.w + b1 * c.z;
+            }
+        }
+        uint4 ra, rb;
+        __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&ra);
+        __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&rb);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            a2[j] = __floats2bfloat162_rn(a[2 * j], a[2 * j + 1]);
+            b2[j] = __floats2bfloat162_rn(b[2 * j], b[2 * j + 1]);
+        }
+        bf16* p = row + (size_t)head * hd;
+        *reinterpret_cast<uint4*>(p + i0) = ra;
+        *reinterpret_cast<uint4*>(p + half + i0) = rb;
+        if (crow >= 0 && (is_k || is_v)) {
+            const int g = is_k ? head - n_q : head - n_q - n_kv;
+            bf16* dst = (is_k ? k_pages : v_pages) +
+                        (((size_t)(crow / page_size) * n_kv + g) * page_size + crow % page_size) * hd;
+            *reinterpret_cast<uint4*>(dst + i0) = ra;
+            *reinterpret_cast<uint4*>(dst + half + i0) = rb;
+        }
+    }
+}
+
+// parts: [n_parts] float slices of (tokens, (n_q + 2 n_kv) * hd), part_stride elements apart; qkv: bfloat16 rows of
+// ld_out elements.  The rotation covers the whole head (cos_sin [position][hd / 2], null: none).
+BROLM_API int brolm_rope_kv_write_parts(const void* parts, int n_parts, long long part_stride, void* qkv, int ld_out,
+                                        const void* positions, const void* cos_sin, int n_q, int n_kv, int hd,
+                                        void* k_pages, void* v_pages, const void* cache_rows, int page_size,
+                                        int tokens, cudaStream_t stream) {
+    if (tokens <= 0) return BROLM_OK;
+    if (n_parts < 1 || hd <= 0 || hd % 16 != 0 || page_size <= 0 || n_q <= 0 || n_kv <= 0) return BROLM_ERR_BAD_SIZE;
+    if (k_pages && (!v_pages || !cache_rows)) return BROLM_ERR_BAD_SIZE;
+    if (((uintptr_t)parts & 15) || ((uintptr_t)qkv & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) ||
+        ((uintptr_t)cos_sin & 15) || ld_out % 8 != 0 || part_stride % 4 != 0)
+        return BROLM_ERR_ALIGNMENT;
+    int items = (n_q + 2 * n_kv) * (hd >> 4);
+    int th = (items + 31) / 32 * 32;
+    if (th > 256) th = 256;
+    return launch_pdl(rope_kv_write_parts_kernel, dim3(tokens), dim3(th), 0, stream, (const float*)parts, n_parts,
+                      part_stride, (bf16*)qkv, ld_out, (const int32_t*)positions, (const float2*)cos_sin, n_q, n_kv, hd,
+                      (bf16*)k_pages, (bf16*)v_pages, (const int32_t*)cache_rows, page_size);
+}
+
 BROLM_API int brolm_rope_kv_write(void* qkv, int dtype, const void* positions, const void* cos_sin, int n_q, int n_kv,
                                   int hd, int rot, void* k_pages, void* v_pages, const void* cache_rows,
                                   int page_size, int tokens, cudaStream_t stream) {

@@ -7,6 +7,7 @@ library fallback: a missing build or a CPU tensor raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 from typing import Optional
 
@@ -177,6 +178,32 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: Optional[
     _check(f(_ptr(qkv), _code(qkv), _ptr(positions), _ptr(cos_sin), n_q, n_kv, head_dim, rotary_dim, _ptr(k_pages),
              _ptr(v_pages), _ptr(cache_rows) if k_pages is not None else None, page_size, qkv.shape[0], _stream()),
            "rope_kv_write")
+
+
+def rope_kv_write_parts(parts: torch.Tensor, qkv: torch.Tensor, positions: torch.Tensor,
+                        cos_sin: Optional[torch.Tensor], n_q: int, n_kv: int, head_dim: int,
+                        k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
+                        cache_rows: Optional[torch.Tensor] = None, page_size: int = 64) -> None:
+    """``rope_kv_write`` for a q/k/v projection that arrives as float32 partial sums of K slices,
+    ``parts`` [slices, tokens, width]: the slices are added in order, q and k rotated over the whole head,
+    and the result rounded once to bfloat16 into ``qkv`` (tokens, width) and into the cache pages."""
+    width = (n_q + 2 * n_kv) * head_dim
+    assert parts.dtype == torch.float32 and parts.dim() == 3 and parts.shape[2] == width and parts.stride(2) == 1
+    assert parts.stride(1) == width and qkv.dtype == torch.bfloat16 and qkv.shape == (parts.shape[1], width)
+    assert qkv.stride(1) == 1 and head_dim % 16 == 0
+    assert positions.dtype == torch.int32 and positions.numel() == qkv.shape[0]
+    if cos_sin is not None:
+        assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1:] == (head_dim // 2, 2)
+    if k_pages is not None:
+        assert v_pages is not None and cache_rows is not None and k_pages.dtype == torch.bfloat16
+        assert k_pages.is_contiguous() and v_pages.is_contiguous()
+        assert tuple(k_pages.shape[1:]) == (n_kv, page_size, head_dim)
+        assert cache_rows.dtype == torch.int32 and cache_rows.numel() == qkv.shape[0]
+    f = _fn("core", "brolm_rope_kv_write_parts", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                                  c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(parts), parts.shape[0], parts.stride(0), _ptr(qkv), qkv.stride(0), _ptr(positions), _ptr(cos_sin),
+             n_q, n_kv, head_dim, _ptr(k_pages), _ptr(v_pages), _ptr(cache_rows) if k_pages is not None else None,
+             page_size, qkv.shape[0], _stream()), "rope_kv_write_parts")
 
 
 def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
@@ -390,6 +417,19 @@ def wait_control(library: str, cycles: int = 0, stall_code: int = 0) -> None:
 
 
 STREAM_MAX_ROWS = 128
+# Up to how many tokens the per-layer products of a step go to the tcgen05 weight stream rather than to the
+# library (cuBLAS).  Measured at the Gemma 2 2B sizes, context 1280 (tokens/s, own stream against library):
+# 24 rows 9,598 / 9,582; 32 rows 12,708 / 12,660; 48 rows 14,076 / 14,436; 64 rows 18,676 / 19,152;
+# 96 rows 20,727 / 22,622; 128 rows 23,901 / 25,584.  With 64 and 128 token columns a stage of the ring is a
+# third and a half tokens, so fewer bytes of weights are in flight per SM; up to 32 it is at least even.
+# BROLM_STREAM_ROWS=128 takes every product of up to 128 tokens to the own kernel, =16 none.
+STREAM_ROWS = int(os.environ.get("BROLM_STREAM_ROWS", "32"))
+
+
+def stream_rows(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether a product of this many tokens is one for the tcgen05 weight stream: more rows than the
+    mma.sync kernel takes (16), at most STREAM_ROWS, operands it takes."""
+    return x.dim() == 2 and SKINNY_MAX_ROWS < x.shape[0] <= STREAM_ROWS and gemm_stream_ok(x, weight)
 
 
 def gemm_stream_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -406,7 +446,9 @@ def gemm_stream_parts(x: torch.Tensor, weight: torch.Tensor, sms: Optional[int] 
     row_tiles = (weight.shape[0] + 127) // 128
     nkb = (x.shape[1] + 63) // 64
     want = max(1, sms // row_tiles)
-    per = max(2, (nkb + want - 1) // want)
+    # at least a ring's worth of K blocks (8) per item: a shorter run is over before its loads are all
+    # in flight, and every further slice is another float copy of the output for the reader to add
+    per = max(min(8, nkb), (nkb + want - 1) // want)
     return max(1, (nkb + per - 1) // per)
 
 
@@ -582,6 +624,6 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
 
 
 __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "device_sms", "wait_control", "embed_scale", "rmsnorm", "residual_rmsnorm",
-           "rope_kv_write", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc2", "gemm_tc2_status", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts",
+           "rope_kv_write", "rope_kv_write_parts", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc2", "gemm_tc2_status", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts", "stream_rows",
            "gemm_stream_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_tc_status", "attention_decode_mma",
            "decode_splits", "argmax", "sample"]

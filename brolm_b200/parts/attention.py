@@ -69,6 +69,15 @@ class Attention(Part):
             qkv = torch.empty((x.shape[0], self.q_dim + 2 * self.kv_dim), dtype=ctx.dtype, device=x.device)
             kernels.skinny_qkv_rope(x, self.w_qkv, qkv, ctx.positions, cos_sin, self.n_q, self.n_kv, self.head_dim,
                                     *kept, page)
+        elif kernels.stream_rows(x, self.w_qkv) and (cos_sin is None or rot == self.head_dim):
+            # 17 to 128 tokens: the weights stream once through tcgen05, cut along K so that every SM takes
+            # part; the kernel that rotates q and k and fills the cache adds the slices on its way
+            slices = kernels.gemm_stream_parts(x, self.w_qkv)
+            sums = torch.empty((slices, x.shape[0], self.q_dim + 2 * self.kv_dim), dtype=torch.float32, device=x.device)
+            kernels.gemm_stream(x, self.w_qkv, sums)
+            qkv = torch.empty((x.shape[0], self.q_dim + 2 * self.kv_dim), dtype=ctx.dtype, device=x.device)
+            kernels.rope_kv_write_parts(sums, qkv, ctx.positions, cos_sin, self.n_q, self.n_kv, self.head_dim, *kept,
+                                        page)
         else:
             qkv = linear(x, self.w_qkv, out_dtype=ctx.dtype)
             kernels.rope_kv_write(qkv, ctx.positions, cos_sin, self.n_q, self.n_kv, self.head_dim, rot, *kept, page)

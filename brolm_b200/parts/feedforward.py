@@ -38,6 +38,9 @@ class GatedFeedForward(Part):
         if kernels.skinny_ok(x, self.w_gate_up):
             # few tokens: both products and the activation in one pass over the weights
             kernels.skinny_gemm(x, self.w_gate_up, act, "gated", self.activation)
+        elif self.inter % 64 == 0 and kernels.stream_rows(x, self.w_gate_up):
+            # 17 to 128 tokens: the same on the tcgen05 weight stream
+            kernels.gemm_stream(x, self.w_gate_up, act, "gated", self.activation)
         elif self.inter % 128 == 0 and kernels.gemm_tc_ok(x, self.w_gate_up, gated=True):
             # many tokens: the activation is the epilogue of the product; [gate | up] never reaches memory
             kernels.gemm_tc(x, self.w_gate_up, act, "gated", self.activation)

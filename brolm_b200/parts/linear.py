@@ -5,10 +5,14 @@ element type in the same way).
 * float32 weight: the framework's own CUDA-core kernel, true 32-bit.
 * bfloat16 weight, up to 16 rows (decode steps): the framework's own
   weight-streaming tensor-core kernel, float32 accumulation.
+* bfloat16 weight, 17 to 128 rows (wider decode batches, short prompts): the
+  framework's tcgen05 weight stream (TMA ring, tokens on the N side of the
+  instruction), float32 accumulation.
 * bfloat16 weight, more rows: the framework's tcgen05 kernel (TMA loads,
   accumulator in tensor memory), float32 accumulation; the library product
   (cuBLAS through torch) only for operands that kernel does not take (a width
-  that is no multiple of 8).  The result is bfloat16 or, on request, float32.
+  that is no multiple of 8) or that leave most SMs without a tile.  The result
+  is bfloat16 or, on request, float32.
 """
 from __future__ import annotations
 
@@ -51,6 +55,17 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
             y = out if out is not None else torch.empty((M, N), dtype=want, device=x.device)
             kernels.skinny_gemm(x, weight, y)
             return y
+        if kernels.stream_rows(x, weight) and want in (torch.bfloat16, torch.float32):
+            # 17 to 128 tokens: still a stream of the weights, on tcgen05 with the tokens on the N side
+            parts = kernels.gemm_stream_parts(x, weight) if (parts_ok and want == torch.float32 and out is None) else 1
+            if parts > 1:
+                y = torch.empty((parts, M, N), dtype=torch.float32, device=x.device)
+                kernels.gemm_stream(x, weight, y)
+                return y
+            y = out if out is not None else torch.empty((M, N), dtype=want, device=x.device)
+            if y.stride(1) == 1:
+                kernels.gemm_stream(x, weight, y)
+                return y
         if kernels.gemm_tc_ok(x, weight) and want in (torch.bfloat16, torch.float32):
             y = out if out is not None else torch.empty((M, N), dtype=want, device=x.device)
             if y.stride(1) == 1 and y.data_ptr() % 16 == 0:

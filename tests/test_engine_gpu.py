@@ -273,10 +273,14 @@ def test_generation_one_step_ahead_equals_step_by_step(setups, graphs, temperatu
 
 
 @pytest.mark.parametrize("name,dtype", CASES)
-@pytest.mark.parametrize("batch", [12, 20])
-def test_decode_in_wider_batches(setups, name, dtype, batch):
-    """Twelve sequences (two token tiles of the few-token products) and twenty (the many-token products
-    take over): unequal prompts together, then token by token, against the plain implementation."""
+@pytest.mark.parametrize("batch", [12, 20, 33, 64, 100])
+def test_decode_in_wider_batches(setups, name, dtype, batch, monkeypatch):
+    """Twelve sequences (two token tiles of the few-token products), then twenty to a hundred (the tcgen05
+    weight stream with 32, 64 and 128 token columns; q/k/v as slices of K that the rotation adds): unequal
+    prompts together, then token by token, against the plain implementation.  (By default more than 32
+    tokens go to the library product; here the own kernel takes them all.)"""
+    from brolm_b200 import kernels
+    monkeypatch.setattr(kernels, "STREAM_ROWS", 128)
     _, config, weights, model = setups[(name, dtype)]
     V = config["vocab_size"]
     g = torch.Generator().manual_seed(batch)

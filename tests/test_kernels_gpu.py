@@ -330,6 +330,46 @@ def test_rope_kv_write_ring(dtype):
     _rope_case(dtype, n_q=2, n_kv=1, hd=32, ring=64, page=32, lengths=[200, 64, 65, 3], seed=8)
 
 
+@pytest.mark.parametrize("n_q,n_kv,hd,slices", [(8, 4, 256, 4), (6, 1, 32, 1), (3, 3, 48, 3), (32, 16, 128, 2)])
+def test_rope_kv_write_from_partial_sums(n_q, n_kv, hd, slices):
+    """The q/k/v projection as float slices of K: added in order, rotated, rounded once, written to the packed
+    row and to the cache; a row with a negative position is left alone."""
+    g = torch.Generator().manual_seed(hd + slices)
+    T, page = 40, 64
+    width = (n_q + 2 * n_kv) * hd
+    parts = torch.randn(slices, T, width, generator=g)
+    positions = torch.randint(0, 500, (T,), generator=g).int()
+    positions[7] = -1
+    theta = 1000.0
+    inv = torch.tensor(theta, dtype=torch.float64) ** (-2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)
+    ang = torch.arange(500, dtype=torch.float64)[:, None] * inv[None]
+    table = torch.stack([ang.cos(), ang.sin()], -1).float()
+    rows = torch.randperm(T * 2, generator=g)[:T].int()          # a place of its own for every token
+    rows[11] = -1                                                 # a token the ring does not keep
+    kp = torch.zeros(3, n_kv, page, hd, dtype=torch.bfloat16, device=DEV)
+    vp = torch.zeros_like(kp)
+    out = torch.full((T, width), 7.0, dtype=torch.bfloat16, device=DEV)
+    kernels.rope_kv_write_parts(parts.to(DEV), out, positions.to(DEV), table.to(DEV), n_q, n_kv, hd, kp, vp,
+                                rows.to(DEV), page)
+    total = parts.double().sum(0)
+    live = positions >= 0
+    pos = positions.clamp(min=0)
+    q_ref = plain.rope(total[:, :n_q * hd], pos, hd, theta)
+    k_ref = plain.rope(total[:, n_q * hd:(n_q + n_kv) * hd], pos, hd, theta)
+    ref = torch.cat([q_ref, k_ref, total[:, (n_q + n_kv) * hd:]], dim=1)
+    close(out[live], ref[live], torch.bfloat16)
+    assert float((out[7].float() - 7.0).abs().max()) == 0.0
+    out, kp, vp = out.cpu(), kp.cpu(), vp.cpu()
+    for t in range(T):
+        if not live[t] or rows[t] < 0:
+            continue
+        pg, place = int(rows[t]) // page, int(rows[t]) % page
+        assert torch.equal(kp[pg, :, place, :].reshape(-1), out[t, n_q * hd:(n_q + n_kv) * hd])
+        assert torch.equal(vp[pg, :, place, :].reshape(-1), out[t, (n_q + n_kv) * hd:])
+    written = (kp.float().abs().sum(-1) > 0).sum()
+    assert int(written) == n_kv * int((live & (rows >= 0)).sum())   # nothing else was touched
+
+
 def test_rope_skips_padding_rows():
     qkv = torch.randn(4, 4 * 16).to(DEV)
     before = qkv.clone()
