@@ -160,7 +160,10 @@ def test_two_engines_of_one_model_with_growing_positions(setups, dtype):
     for i in range(20, 30):
         check(small.step([a], [[p[i]]])[0], ref_p[i], dtype, "first engine, before the second exists")
     large = bb.Engine(model, max_tokens=1024, max_slots=1)            # more positions: the table is made anew
-    filler = [torch.empty(1 << 20, device=DEV) for _ in range(8)]       # whatever was freed is taken again
+    # whatever the second engine's set-up freed is taken again and overwritten: blocks of the old table's size
+    # (the allocator keeps small and large blocks apart) and a few large ones
+    old_bytes = 128 * (config["head_dim"] // 2) * 2 * 4
+    filler = [torch.empty(old_bytes // 4, device=DEV) for _ in range(256)] + [torch.empty(1 << 20, device=DEV) for _ in range(8)]
     for f in filler:
         f.fill_(float("nan"))
     (b,) = large.open(1)
