@@ -157,6 +157,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
     // Units go through the ring in the order of their use: K(0); then K(j+1), V(j) for every tile j.
     if (warp == 0) {
         if (lane == 0 && n_tiles > 0) {
+            // Launched with programmatic stream serialization: the block may be here while the kernel before it
+            // (the rotation that writes q and k) still runs.  Nothing of this kernel touches memory before its
+            // first tiles have arrived, so the loader's wait is the kernel's.
+            pdl_wait();
             mbar_expect_tx(bar(Q_FULL), SH::Q_BYTES);
             for (int d = 0; d < DB; ++d)
                 tma_load_3d(q_s + d * (BM * 128), &map_q, d * 64, g * a.group, q0 + tok0, bar(Q_FULL));
@@ -194,6 +198,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
                 if (j + 1 < n_tiles) load_k(j + 1);
                 if (ok) load_v(j);
             }
+            pdl_trigger();         // every tile is asked for: the next kernel may move in
             if (*give_up) {        // let the loads in flight land before the block goes away
                 drain_on(bar(Q_FULL), 0, give_up, 9);
                 for (int i = max(0, u - SLOTS); i < u; ++i) drain_on(bar(U_FULL + i % SLOTS), (i / SLOTS) & 1, give_up, 9);
@@ -413,8 +418,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
-    attn_prefill_tc_kernel<HD><<<grid, THREADS, smem, stream>>>(mq, mk, mv, a);
-    return launch_status();
+    return launch_pdl(attn_prefill_tc_kernel<HD>, grid, dim3(THREADS), smem, stream, mq, mk, mv, a);
 }
 
 }  // namespace

@@ -107,6 +107,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
         if (lane == 0) {
             int it = 0;                                   // stages filled so far, over all tiles
             bool ok = true;
+            pdl_wait();                                   // (nothing of this kernel touches memory before its first operands)
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int m_tile = tile % g.m_tiles, n_tile = tile / g.m_tiles;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -124,6 +125,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
                     }
                 }
             }
+            pdl_trigger();
             if (*give_up) {
                 // let the loads that are still in flight land before the block goes away
                 for (int j = max(0, it - STAGES); j < it; ++j)
@@ -238,8 +240,7 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& g, cuda
         raised = true;
     }
     const int tiles = g.m_tiles * g.n_tiles;
-    gemm_tc_kernel<EPI><<<tiles < sms ? tiles : sms, THREADS, SMEM_BYTES, stream>>>(mx, mw, g);
-    return launch_status();
+    return launch_pdl(gemm_tc_kernel<EPI>, dim3(tiles < sms ? tiles : sms), dim3(THREADS), SMEM_BYTES, stream, mx, mw, g);
 }
 
 }  // namespace

@@ -128,6 +128,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (lane == 0) {
             int it = 0;
             bool ok = !*give_up;
+            // Launched with programmatic stream serialization: the block may be here while the kernel before
+            // it still runs.  Nothing of this kernel touches memory before its first operands have arrived,
+            // so the loader's wait is the kernel's.
+            pdl_wait();
             for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
                 const int m_tile = tile % g.m_tiles, n_tile = tile / g.m_tiles;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -142,6 +146,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         tma_load_2d_pair(b_dst, &map_w, kb * BK, n_tile * BN + (int)rank * HN, full);
                 }
             }
+            pdl_trigger();                                  // the operands are asked for: the next kernel may move in
             if (*give_up && rank == 0) {
                 for (int j = max(0, it - STAGES); j < it; ++j)
                     drain_on(full0 + 8 * (j % STAGES), (j / STAGES) & 1, give_up, 4);
@@ -248,8 +253,7 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& g, cuda
     }
     const int tiles = g.m_tiles * g.n_tiles;
     const int pairs = tiles < sms / 2 ? tiles : sms / 2;
-    gemm_tc2_kernel<EPI><<<2 * pairs, THREADS, SMEM_BYTES, stream>>>(mx, mw, g);
-    return launch_status();
+    return launch_pdl(gemm_tc2_kernel<EPI>, dim3(2 * pairs), dim3(THREADS), SMEM_BYTES, stream, mx, mw, g);
 }
 
 }  // namespace

@@ -174,6 +174,8 @@ class Engine:
         self._graphs_generation = model.generation
         self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
         self.last_h2d_bytes = 0          # bytes the last step copied from the host
+        self._pin: Optional[torch.Tensor] = None      # pinned staging buffer of the steps that are not captured
+        self._pin_copied = None
 
     # slots ----------------------------------------------------------------
     def open(self, n: int = 1) -> list[int]:
@@ -325,11 +327,25 @@ class Engine:
         parts += [cache.write_rows(g, plan.slots, plan.old, plan.new_len) for g in range(len(tables))]
         sizes = [p.size for p in parts]
         offs = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])
-        host = torch.zeros(int(offs[-1]), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        n = int(offs[-1])
+        if self.device.type == "cuda":
+            # one pinned buffer for the engine's life (allocating pinned memory costs more than filling it);
+            # the copy of the step before must have left it before it is written again
+            if self._pin is None or self._pin.numel() < n:
+                self._pin = torch.zeros(max(n, 4096), dtype=torch.int32, pin_memory=True)
+                self._pin_copied = torch.cuda.Event()
+            else:
+                self._pin_copied.synchronize()
+            host = self._pin[:n]
+        else:
+            host = torch.zeros(n, dtype=torch.int32)
         hv = host.numpy()
+        hv[:] = 0
         for p, o in zip(parts, offs[:-1]):
             hv[o:o + p.size] = p
         dev = host.to(self.device, non_blocking=True)
+        if self.device.type == "cuda":
+            self._pin_copied.record()
         self.last_h2d_bytes = host.numel() * 4
         seg = [dev[int(o):int(o) + s] for o, s in zip(offs[:-1], sizes)]
         page_tables = [seg[7 + g].view(B, tables[g].shape[1]) for g in range(len(tables))]

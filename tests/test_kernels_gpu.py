@@ -243,7 +243,9 @@ def test_gemm_stream_gated(M, F, K, act):
     ref = (plain.gelu_tanh(gate) if act == "gelu_tanh" else gate * torch.sigmoid(gate)) * up
     close(out, ref, torch.bfloat16)
     assert kernels.gemm_stream_status() == 0
-    assert kernels.gemm_stream_parts(torch.empty(8, 2048), torch.empty(2304, 2048)) == 8
+    # o of Gemma 2 2B (32 blocks of K, 18 row tiles): a ring's worth of K per item, four slices
+    assert kernels.gemm_stream_parts(torch.empty(8, 2048), torch.empty(2304, 2048)) == 4
+    assert kernels.gemm_stream_parts(torch.empty(8, 9216), torch.empty(2304, 9216)) == 8
     assert kernels.gemm_stream_parts(torch.empty(8, 2304), torch.empty(256000, 2304)) == 1
 
 
