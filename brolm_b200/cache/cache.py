@@ -216,6 +216,7 @@ class Cache:
                    rows: Optional[int] = None) -> torch.Tensor:
         """Host int32 table [rows or len(slots), width] of the slots' pages; a
         negative slot (padding row) and unused places read as page 0."""
+        import numpy as np
         g = self.kv_groups[group_id]
         lists = [g.pages[s] if s >= 0 else [] for s in slots]
         w = max([len(l) for l in lists] + [1])
@@ -223,11 +224,11 @@ class Cache:
             if width < w:
                 raise CacheError("page table width is too small")
             w = width
-        table = torch.zeros((rows or len(slots), w), dtype=torch.int32)
+        table = np.zeros((rows or len(slots), w), dtype=np.int32)
         for r, l in enumerate(lists):
             if l:
-                table[r, :len(l)] = torch.tensor(l, dtype=torch.int32)
-        return table
+                table[r, :len(l)] = l
+        return torch.from_numpy(table)
 
     def write_rows(self, group_id: int, slots: Sequence[int], old: Sequence[int], new: Sequence[int]):
         """Where each new token of a step goes in a group's storage: one int per

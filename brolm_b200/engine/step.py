@@ -281,7 +281,7 @@ class Engine:
             raise StepError("step: a slot is named twice")
         cache = self.cache
         old = [cache.length(s) for s in slots]
-        n_new = [len(t) for t in tokens]
+        n_new = [len(t) for t in tokens]         # (lists, NumPy arrays and host tensors all have a length)
         if min(n_new) <= 0:
             raise StepError("step: every sequence must bring at least one token")
         if all(o == 0 for o in old):
@@ -295,7 +295,10 @@ class Engine:
         if max(new_len) > cache.max_positions:
             raise StepError(f"step: a sequence would reach {max(new_len)} tokens; the cache was made for "
                             f"sequences of up to {cache.max_positions}")
-        flat = np.fromiter((t for seq in tokens for t in seq), dtype=np.int64, count=sum(n_new))
+        try:
+            flat = np.concatenate([np.asarray(seq, dtype=np.int64).reshape(-1) for seq in tokens])
+        except (TypeError, ValueError, OverflowError):
+            raise StepError("step: tokens must be sequences of integer ids") from None
         if flat.min() < 0 or flat.max() >= self.vocab:
             raise StepError(f"step: token id out of range [0, {self.vocab})")
         if want is None:

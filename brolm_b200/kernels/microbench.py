@@ -3,6 +3,9 @@
     python -m brolm_b200.kernels.microbench attn_decode --batch 8 --ctx 8192 [--window 4096]
     python -m brolm_b200.kernels.microbench attn_prefill --tokens 2048
     python -m brolm_b200.kernels.microbench norms --batch 8
+    python -m brolm_b200.kernels.microbench stream --batch 64            (the weight stream against the library)
+    python -m brolm_b200.kernels.microbench timeline_decode --batch 8 --ctx 8192 --layers 6
+    python -m brolm_b200.kernels.microbench timeline_prefill --tokens 2048 --layers 4
 
 Sizes default to those of Gemma 2 2B (8 query heads, 4 kv heads of 256).  Inputs
 are larger than the L2 cache or the L2 is flushed between repetitions.
@@ -182,9 +185,86 @@ def norms(args) -> None:
     print(f"rmsnorm rows={B} hidden={H}: {ms * 1e3:.1f} us")
 
 
+def _print_timeline(events, first: int, title: str) -> None:
+    ev = events[first:]
+    t0 = ev[0].time_range.start
+    prev_end = t0
+    print(title)
+    print("   start     time  gap to the end of all kernels before   kernel (microseconds)")
+    for e in ev:
+        start, dur = e.time_range.start - t0, e.time_range.end - e.time_range.start
+        name = e.name.replace("void ", "").replace("(anonymous namespace)::", "").replace("<unnamed>::", "")[:64]
+        print(f"{start:8.2f} {dur:8.2f} {e.time_range.start - prev_end:8.2f}  {name}")
+        prev_end = max(prev_end, e.time_range.end)
+    print(f"total {prev_end - t0:.1f} us")
+
+
+def _cuda_events(fn):
+    """Device activity records (CUPTI, through torch.profiler) of what ``fn`` launches: every kernel with its
+    start and end on the device's own clock, captured steps included.  Unlike ncu nothing is serialised, so
+    the overlap of kernels launched with programmatic stream serialization shows (negative gaps); the
+    records cost a little time per kernel, so the figures are for comparing shares, not for quoting."""
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        fn()
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    ev.sort(key=lambda e: e.time_range.start)
+    return ev
+
+
+def timeline_decode(args) -> None:
+    """One captured decode step of a model of Gemma 2 2B's layer sizes (--layers of them), kernel by kernel."""
+    import brolm_b200 as bb
+    B, ctx = args.batch, args.ctx
+    cfg = bb.Gemma2Config(num_hidden_layers=args.layers)
+    model = bb.Model(cfg, dtype="bfloat16", device=DEV).init_random(seed=0, on_device=True)
+    eng = bb.Engine(model, max_tokens=B * ((ctx + 63) // 64 * 64), max_slots=B, max_seq_len=ctx)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab_size, (ctx - 40,), generator=g).tolist() for _ in range(B)]
+    slots = eng.open(B)
+    sampler = bb.Sampler(bb.SamplingParams(temperature=0.0))
+    streams = torch.arange(B, dtype=torch.int32, device=DEV)
+    ids = sampler(eng.step(slots, prompts), streams, 0)
+    pick = list(range(B))
+    state = {"ids": ids, "n": 1}
+
+    def steps(n):
+        for _ in range(n):
+            state["ids"] = sampler(eng.step_from(slots, state["ids"], pick), streams, state["n"])
+            state["n"] += 1
+
+    steps(20)
+    torch.cuda.synchronize()
+    ev = _cuda_events(lambda: steps(3))
+    first = [i for i, e in enumerate(ev) if "embed" in e.name][-1]
+    _print_timeline(ev, first, f"decode step, batch {B}, context {ctx}, {args.layers} layers of the Gemma 2 2B sizes")
+
+
+def timeline_prefill(args) -> None:
+    """One prompt of --tokens tokens through --layers layers of the Gemma 2 2B sizes, kernel by kernel."""
+    import brolm_b200 as bb
+    cfg = bb.Gemma2Config(num_hidden_layers=args.layers)
+    model = bb.Model(cfg, dtype="bfloat16", device=DEV).init_random(seed=0, on_device=True)
+    eng = bb.Engine(model, max_tokens=args.tokens + 64, max_slots=1)
+    prompt = torch.randint(0, cfg.vocab_size, (args.tokens,), generator=torch.Generator().manual_seed(1)).tolist()
+
+    def run():
+        (s,) = eng.open(1)
+        eng.step([s], [prompt])
+        eng.close([s])
+
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    ev = _cuda_events(run)
+    _print_timeline(ev, 0, f"prompt of {args.tokens} tokens, {args.layers} layers of the Gemma 2 2B sizes")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "model_prefill", "norms", "skinny", "gemm", "stream"])
+    ap.add_argument("what", choices=["attn_decode", "attn_prefill", "model_prefill", "norms", "skinny", "gemm", "stream",
+                                     "timeline_decode", "timeline_prefill"])
     ap.add_argument("--inter", type=int, default=9216)
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--batch", type=int, default=8)
@@ -204,7 +284,8 @@ def main() -> None:
         from .. import kernels
         kernels.USE_TC_GEMM = False
     {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "model_prefill": model_prefill,
-     "norms": norms, "skinny": skinny, "gemm": gemm, "stream": stream}[args.what](args)
+     "norms": norms, "skinny": skinny, "gemm": gemm, "stream": stream,
+     "timeline_decode": timeline_decode, "timeline_prefill": timeline_prefill}[args.what](args)
 
 
 if __name__ == "__main__":
