@@ -14,10 +14,11 @@ from .config import ConfigError, Gemma2Config, ModelConfig, load_config, registe
 from .engine import DecoderModel, Engine, StepError, generate, load_model, write_random_model
 from .parts import register_part
 from .sampling import GenerateOptions, SamplingParams, Sampler
+from .tokenizer import GemmaTokenizer
 from .weights import WeightsError
 
 Model = DecoderModel
 
 __all__ = ["ConfigError", "Gemma2Config", "ModelConfig", "load_config", "register_architecture", "DecoderModel",
            "Model", "Engine", "StepError", "load_model", "write_random_model", "register_part", "WeightsError", "generate", "GenerateOptions", "SamplingParams",
-           "Sampler"]
+           "Sampler", "GemmaTokenizer"]

@@ -4,14 +4,17 @@ Options are named as in wlejon/brolm's text tools
 (tools/run_mistral_text.cpp:63-82): --max-new, --temp (<= 0: greedy, the
 default), --top-k, --top-p, --seed, --no-bos.  A model comes from --model DIR
 (config.json + safetensors) or from --random with the sizes of a config.json
-given by --config.  The interface is token ids (--ids or --ids-file, one
-request per line); brolm's tokenizer for this family
-(src/gemma_tokenizer.cpp) is outside this library, so --prompt TEXT is
-refused with a pointer to --ids.
+given by --config.  Prompts are token ids (--ids or --ids-file, one request
+per line) or text (--prompt TEXT, may be repeated) with the family's
+tokenizer: --tok tokenizer.json, by default the tokenizer.json in the model
+folder (brolm src/gemma_tokenizer.cpp; --chat wraps the text in Gemma's turn
+markers as brolm's tools wrap theirs in the family's chat template).  With a
+tokenizer the completions are printed as text as well.
 """
 from __future__ import annotations
 
 import argparse
+import os
 import sys
 import tempfile
 import time
@@ -29,7 +32,9 @@ def main(argv=None) -> int:
     ap.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights")
     ap.add_argument("--ids", action="append", help="prompt token ids, e.g. 2,651,6037 (may be repeated)")
     ap.add_argument("--ids-file", help="file with one prompt per line, ids separated by spaces or commas")
-    ap.add_argument("--prompt", help="not available: this library takes token ids")
+    ap.add_argument("--prompt", action="append", help="prompt text (needs a tokenizer; may be repeated)")
+    ap.add_argument("--tok", help="tokenizer.json (default: the one in the --model folder)")
+    ap.add_argument("--chat", action="store_true", help="wrap --prompt in Gemma's <start_of_turn> chat markers")
     ap.add_argument("--max-new", type=int, default=48, help="max new tokens (default 48)")
     ap.add_argument("--temp", type=float, default=0.0, help="sampling temperature, <=0 => greedy (default 0)")
     ap.add_argument("--top-k", type=int, default=0, help="top-k cutoff, 0 = off")
@@ -43,19 +48,32 @@ def main(argv=None) -> int:
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
-    if args.prompt is not None:
-        print("error: --prompt needs a tokenizer, which this library does not have; pass token ids with --ids",
-              file=sys.stderr)
+    if bool(args.model) == bool(args.random):
+        print("error: pass exactly one of --model DIR and --random", file=sys.stderr)
         return 2
+    tokenizer = None
+    tok_path = args.tok or (os.path.join(args.model, "tokenizer.json") if args.model else None)
+    if args.prompt or args.tok:
+        if not tok_path or not os.path.exists(tok_path):
+            print(f"error: tokenizer not found at {tok_path} (pass --tok tokenizer.json, or token ids with --ids)",
+                  file=sys.stderr)
+            return 2
+        from .tokenizer import GemmaTokenizer, TokenizerError
+        try:
+            tokenizer = GemmaTokenizer.load(tok_path)
+        except TokenizerError as e:
+            print(f"error: {e}", file=sys.stderr)
+            return 2
     prompts = [parse_ids(t) for t in (args.ids or [])]
     if args.ids_file:
         with open(args.ids_file) as fh:
             prompts += [parse_ids(line) for line in fh if line.strip()]
+    for text in args.prompt or []:
+        if args.chat:
+            text = f"<start_of_turn>user\n{text}<end_of_turn>\n<start_of_turn>model\n"
+        prompts.append(tokenizer.tokenize(text))            # <bos> is put in front below, unless --no-bos
     if not prompts:
-        print("error: no prompt; pass --ids or --ids-file", file=sys.stderr)
-        return 2
-    if bool(args.model) == bool(args.random):
-        print("error: pass exactly one of --model DIR and --random", file=sys.stderr)
+        print("error: no prompt; pass --prompt, --ids or --ids-file", file=sys.stderr)
         return 2
 
     import brolm_b200 as bb
@@ -90,6 +108,9 @@ def main(argv=None) -> int:
             print(" ".join(map(str, p)))
             print("--- completion ---")
             print(" ".join(map(str, o)))
+            if tokenizer is not None:
+                print("--- text ---")
+                print(tokenizer.decode(o))
             print(f"[info] generated {len(o)} tokens")
         total = sum(len(o) for o in outs)
         print(f"[info] {total} tokens in {dt:.2f} s ({total / max(dt, 1e-9):.1f} tokens/s, first call includes "

@@ -185,6 +185,15 @@ def norms(args) -> None:
     print(f"rmsnorm rows={B} hidden={H}: {ms * 1e3:.1f} us")
 
 
+def _config(args):
+    """The Gemma 2 configuration of --layers layers with the layer sizes given on the command line
+    (the defaults are those of Gemma 2 2B)."""
+    import brolm_b200 as bb
+    return bb.Gemma2Config(num_hidden_layers=args.layers, hidden_size=args.hidden, intermediate_size=args.inter,
+                           num_attention_heads=args.heads, num_key_value_heads=args.kv_heads, head_dim=args.head_dim,
+                           query_pre_attn_scalar=float(args.scalar or args.head_dim))
+
+
 def _print_timeline(events, first: int, title: str) -> None:
     ev = events[first:]
     t0 = ev[0].time_range.start
@@ -217,7 +226,7 @@ def timeline_decode(args) -> None:
     """One captured decode step of a model of Gemma 2 2B's layer sizes (--layers of them), kernel by kernel."""
     import brolm_b200 as bb
     B, ctx = args.batch, args.ctx
-    cfg = bb.Gemma2Config(num_hidden_layers=args.layers)
+    cfg = _config(args)
     model = bb.Model(cfg, dtype="bfloat16", device=DEV).init_random(seed=0, on_device=True)
     eng = bb.Engine(model, max_tokens=B * ((ctx + 63) // 64 * 64), max_slots=B, max_seq_len=ctx)
     g = torch.Generator().manual_seed(1)
@@ -238,13 +247,13 @@ def timeline_decode(args) -> None:
     torch.cuda.synchronize()
     ev = _cuda_events(lambda: steps(3))
     first = [i for i, e in enumerate(ev) if "embed" in e.name][-1]
-    _print_timeline(ev, first, f"decode step, batch {B}, context {ctx}, {args.layers} layers of the Gemma 2 2B sizes")
+    _print_timeline(ev, first, f"decode step, batch {B}, context {ctx}, {args.layers} layers, hidden {args.hidden}")
 
 
 def timeline_prefill(args) -> None:
     """One prompt of --tokens tokens through --layers layers of the Gemma 2 2B sizes, kernel by kernel."""
     import brolm_b200 as bb
-    cfg = bb.Gemma2Config(num_hidden_layers=args.layers)
+    cfg = _config(args)
     model = bb.Model(cfg, dtype="bfloat16", device=DEV).init_random(seed=0, on_device=True)
     eng = bb.Engine(model, max_tokens=args.tokens + 64, max_slots=1)
     prompt = torch.randint(0, cfg.vocab_size, (args.tokens,), generator=torch.Generator().manual_seed(1)).tolist()
@@ -258,7 +267,7 @@ def timeline_prefill(args) -> None:
         run()
     torch.cuda.synchronize()
     ev = _cuda_events(run)
-    _print_timeline(ev, 0, f"prompt of {args.tokens} tokens, {args.layers} layers of the Gemma 2 2B sizes")
+    _print_timeline(ev, 0, f"prompt of {args.tokens} tokens, {args.layers} layers, hidden {args.hidden}")
 
 
 def main() -> None:
@@ -275,6 +284,7 @@ def main() -> None:
     ap.add_argument("--kv-heads", type=int, default=4)
     ap.add_argument("--head-dim", type=int, default=256)
     ap.add_argument("--hidden", type=int, default=2304)
+    ap.add_argument("--scalar", type=float, default=0.0, help="query_pre_attn_scalar (0: head_dim)")
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--cap", type=float, default=50.0, help="soft cap of the attention scores (0: none)")
     ap.add_argument("--reps", type=int, default=20)
