@@ -37,10 +37,22 @@
 // scale, cap * tanh(s / cap), mask, softmax).  Key j is visible from position p
 // iff 0 <= p - j < window.
 //
+// A prompt of a model with few kv heads gives few blocks, and causal blocks of very different lengths
+// (1 to 16 key tiles at 2,048 tokens).  The launcher then cuts the row blocks with the most key tiles
+// in two along the keys (brolm_attn_prefill_tc_plan decides how many, by laying the blocks out over
+// the SMs in the order in which they start): both halves write their unnormalised accumulator and
+// their (reference maximum, sum) as float partial results, take a ticket, and the half that comes
+// second merges the other's partial result into its own and writes the rows.  No block waits for
+// another.
+//
 // Every mbarrier wait is bounded; a wait that runs out records a code that
 // brolm_attn_tc_status() returns, lets outstanding loads land, frees the tensor
 // memory and returns (the launch's results are then not valid).
 #include "tcgen05.cuh"
+
+#include <algorithm>
+#include <functional>
+#include <vector>
 
 namespace {
 
@@ -61,7 +73,14 @@ struct TcArgs {
     float scale, cap;
     int window;
     uint32_t v_lbo, v_sbo;      // descriptor strides of the value operand, in 16-byte units
+    int n_split;                // the heaviest n_split row blocks of every (sequence, kv head) run as two halves of their keys
+    float* part_o;              // [pair][2][hd / 4][BM][4] unnormalised accumulators of the halves
+    float* part_ml;             // [pair][2][BM][2] reference maximum (log2 units) and sum
 };
+
+// One ticket per pair of halves; the half that comes second sets it back to zero.
+constexpr int MAX_PAIRS = 1024;
+__device__ int g_pair_tickets[MAX_PAIRS];
 
 using namespace tc;
 
@@ -109,16 +128,23 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
     uint64_t* bars = reinterpret_cast<uint64_t*>(base + SH::Q_BYTES + SLOTS * SH::SLOT);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
     volatile int* give_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars + N_BARS) + 16);   // [2][2][BM]: maxima by tile parity and half; the sums reuse it
+    int* ticket_s = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars + N_BARS) + 16);
+    float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars + N_BARS) + 32);   // [2][2][BM]: maxima by tile parity and half; the sums reuse it
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * i; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // heaviest row blocks first
+    // Blocks start in the order of their linear index (x fastest); the blocks with the most key tiles come
+    // first, over all sequences and kv heads: rank 0 is the last row block.  The first 2 * n_split ranks are
+    // the halves of the n_split heaviest row blocks.
     const int per_x = gridDim.y * gridDim.z;
-    const int n = blockIdx.x * per_x + blockIdx.z * gridDim.y + blockIdx.y;
-    const int xt = gridDim.x - 1 - n / per_x;
-    const int b = (n % per_x) / gridDim.y, g = (n % per_x) % gridDim.y;
+    const int d = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    const int rank = d / per_x, which = d % per_x;
+    const int b = which / gridDim.y, g = which % gridDim.y;
+    const int row_tiles = gridDim.x - a.n_split;
+    int part = rank < 2 * a.n_split ? (rank & 1) : -1;   // 0, 1: a half; -1: the whole row block
+    const int xt = part >= 0 ? row_tiles - 1 - (rank >> 1) : row_tiles - 1 - (rank - a.n_split);
+    const int pair = (rank >> 1) * per_x + which;
     const int q0 = a.cu_q[b], q_len = a.cu_q[b + 1] - q0;
     const int n_rows = q_len * a.group;
     const int row0 = xt * BM;
@@ -127,8 +153,18 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
     const int window = a.window > 0 ? a.window : 0x3fffffff;
     const int tok0 = row0 / a.group;                     // BM is a multiple of the group
     const int tok_hi = active ? (row0 + rows_here - 1) / a.group : 0;
-    const int t_first = active ? max(0, tok0 - window + 1) / BN : 0;
-    const int n_tiles = active ? tok_hi / BN - t_first + 1 : 0;
+    int t_first = active ? max(0, tok0 - window + 1) / BN : 0;
+    int n_tiles = active ? tok_hi / BN - t_first + 1 : 0;
+    if (part >= 0) {
+        if (n_tiles < 2) {                  // nothing to cut: the first half does the row block alone
+            if (part == 1) n_tiles = 0;
+            part = -1;
+        } else {                            // the second half gets the tile on the diagonal and the odd one
+            const int first_half = n_tiles / 2;
+            if (part == 1) t_first += first_half;
+            n_tiles = part == 1 ? n_tiles - first_half : first_half;
+        }
+    }
 
     if (threadIdx.x == 0) {
         mbar_init(bar(Q_FULL), 1);
@@ -365,28 +401,98 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
         const int fin = (n_tiles & 1) * 2;                  // the buffer the next tile would have used
         xch[(fin + half) * BM + r] = l;
         asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-        if (ok) {
-            fence_after_sync();
-            const float total = xch[fin * BM + r] + xch[(fin + 1) * BM + r];
-            const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+        if (ok) fence_after_sync();
+        const float total = xch[fin * BM + r] + xch[(fin + 1) * BM + r];
+        // A half: the partial result goes to memory, then the ticket says whether the other half is done.
+        // (Every softmax warp takes part in the two barriers, whatever its waits did: a block that gave up
+        // has already made the launch invalid.)
+        float own = 1.0f, theirs = 0.0f, sum_all = total;
+        const float4* their_o = nullptr;
+        bool writes = true;
+        if (part >= 0) {
+            // A half's accumulator lies in memory as [head size / 4][row][4 floats]: the 32 rows of a warp write
+            // 512 consecutive bytes per instruction, and the thread of the other half that owns the same row
+            // and columns reads them back in the same way.
+            float4* my_o = reinterpret_cast<float4*>(a.part_o) + (size_t)(pair * 2 + part) * (HD / 4) * BM + r;
+            if (ok) {
+#pragma unroll 1
+                for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
+                    uint32_t ov[32];
+                    tmem_ld32(tmem + lane_addr + O_COL + c, ov);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        my_o[(size_t)((c + i) / 4) * BM] = make_float4(__uint_as_float(ov[i]), __uint_as_float(ov[i + 1]),
+                                                                         __uint_as_float(ov[i + 2]), __uint_as_float(ov[i + 3]));
+                }
+                if (half == 0) {
+                    float* ml = a.part_ml + ((size_t)(pair * 2 + part) * BM + r) * 2;
+                    ml[0] = m_ref;
+                    ml[1] = total;
+                }
+            }
+            __threadfence();
+            asm volatile("bar.sync 5, 256;" ::: "memory");
+            if (threadIdx.x == 64) *ticket_s = atomicAdd(&g_pair_tickets[pair], 1);
+            asm volatile("bar.sync 5, 256;" ::: "memory");
+            if (*ticket_s == 0) {
+                writes = false;                             // the other half will find this one's result
+            } else {
+                if (threadIdx.x == 64) g_pair_tickets[pair] = 0;
+                const float2 other = __ldcg(reinterpret_cast<const float2*>(a.part_ml) + (size_t)(pair * 2 + (part ^ 1)) * BM + r);
+                const float m_o = other.x, l_o = other.y;
+                const float m_all = fmaxf(m_ref, m_o);
+                if (m_all > -INFINITY) {                    // (a half that saw nothing of a row: 2^(-inf) = 0)
+                    own = fast_exp2(m_ref - m_all);
+                    theirs = fast_exp2(m_o - m_all);
+                } else {
+                    own = theirs = 0.0f;
+                }
+                sum_all = total * own + l_o * theirs;
+                their_o = reinterpret_cast<const float4*>(a.part_o) + (size_t)(pair * 2 + (part ^ 1)) * (HD / 4) * BM + r;
+            }
+        }
+        if (ok && writes) {
+            const float inv = sum_all > 0.0f ? 1.0f / sum_all : 0.0f;
+            const float k_own = own * inv, k_theirs = theirs * inv;
             const int row = row0 + r, tok = row / a.group, head = g * a.group + row % a.group;
             bf16* dst = a.out + (size_t)(q0 + tok) * a.out_stride + (size_t)head * HD;
+            // the other half's values: a piece of 32 is asked for while the piece before it is merged and stored
+            const bool merge = their_o != nullptr && row_ok;
+            float4 th[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                th[i] = merge ? __ldcg(their_o + (size_t)(half * (HD / 8) + i) * BM) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll 1
             for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
+                float4 tn[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    tn[i] = (merge && c + 32 < (half + 1) * (HD / 2)) ? __ldcg(their_o + (size_t)((c + 32) / 4 + i) * BM)
+                                                                     : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 uint32_t ov[32];
                 tmem_ld32(tmem + lane_addr + O_COL + c, ov);
                 tmem_wait_ld();
                 if (row_ok) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
+                        const float4 t0 = th[i / 4], t1 = th[i / 4 + 1];
+                        float f[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(ov[i + e]) * k_own;
+                        f[0] = fmaf(t0.x, k_theirs, f[0]); f[1] = fmaf(t0.y, k_theirs, f[1]);
+                        f[2] = fmaf(t0.z, k_theirs, f[2]); f[3] = fmaf(t0.w, k_theirs, f[3]);
+                        f[4] = fmaf(t1.x, k_theirs, f[4]); f[5] = fmaf(t1.y, k_theirs, f[5]);
+                        f[6] = fmaf(t1.z, k_theirs, f[6]); f[7] = fmaf(t1.w, k_theirs, f[7]);
                         uint4 pk;
                         __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            p2[e] = __floats2bfloat162_rn(__uint_as_float(ov[i + 2 * e]) * inv, __uint_as_float(ov[i + 2 * e + 1]) * inv);
+                        for (int e = 0; e < 4; ++e) p2[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
                         *reinterpret_cast<uint4*>(dst + c + i) = pk;
                     }
                 }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) th[i] = tn[i];
             }
         }
     }
@@ -410,7 +516,7 @@ template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcArgs& a, dim3 grid,
            cudaStream_t stream) {
     using SH = Shape<HD>;
-    constexpr size_t smem = (size_t)SH::Q_BYTES + (size_t)SH::SLOTS * SH::SLOT + N_BARS * 8 + 16 + 4 * BM * 4;
+    constexpr size_t smem = (size_t)SH::Q_BYTES + (size_t)SH::SLOTS * SH::SLOT + N_BARS * 8 + 32 + 4 * BM * 4;
     static_assert(smem <= 232448, "shared memory of a block");
     static bool raised = false;
     if (!raised) {
@@ -423,18 +529,85 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 
 }  // namespace
 
+// How many of the heaviest row blocks of every (sequence, kv head) to cut in two along the keys, for
+// prompts of max_q_len tokens (all taken to be that long).  Blocks are laid out over the SMs in the order
+// in which they start (each to the SM that is free first), a block costing its key tiles plus a fixed
+// start, a half also the merge; the candidate with the shortest schedule wins, none when the blocks
+// already outnumber the SMs twice over.  Returns 0 .. row blocks; pairs = result * n_kv * batch.
+BROLM_API int brolm_attn_prefill_tc_plan(int max_q_len, int n_kv, int group, int window, int batch) {
+    if (max_q_len <= 0 || n_kv <= 0 || group <= 0 || batch <= 0 || BM % group != 0) return 0;
+    const int sms = device_sm_count();
+    const long long per_x = (long long)n_kv * batch;
+    const int rows = max_q_len * group, row_tiles = (rows + BM - 1) / BM;
+    if (row_tiles * per_x >= 2LL * sms || row_tiles < 2) return 0;
+    struct Key { int q, kv, group, window, batch, sms, result; };
+    static Key memo[8];
+    static int memo_next = 0;
+    for (const Key& k : memo)
+        if (k.q == max_q_len && k.kv == n_kv && k.group == group && k.window == window && k.batch == batch && k.sms == sms)
+            return k.result;
+    const int w = window > 0 ? window : 0x3fffffff;
+    std::vector<int> tiles(row_tiles);                              // by rank: the last row block first
+    for (int rank = 0; rank < row_tiles; ++rank) {
+        const int xt = row_tiles - 1 - rank;
+        const int tok0 = xt * BM / group, tok_hi = (std::min(rows, (xt + 1) * BM) - 1) / group;
+        tiles[rank] = tok_hi / BN - std::max(0, tok0 - w + 1) / BN + 1;
+    }
+    const float START = 2.4f, MERGE = 2.0f;                         // in key tiles (2.5 us each at head size 256): measured
+    std::vector<float> free_at(sms);
+    auto schedule = [&](int n_split) {
+        std::fill(free_at.begin(), free_at.end(), 0.0f);
+        std::make_heap(free_at.begin(), free_at.end(), std::greater<float>());
+        float end = 0.0f;
+        auto run = [&](float cost) {
+            std::pop_heap(free_at.begin(), free_at.end(), std::greater<float>());
+            const float t = free_at.back() + cost;
+            free_at.back() = t;
+            std::push_heap(free_at.begin(), free_at.end(), std::greater<float>());
+            end = std::max(end, t);
+        };
+        for (int rank = 0; rank < row_tiles; ++rank) {
+            const int t = tiles[rank];
+            if (rank < n_split && t >= 2) {
+                for (int h = 0; h < 2; ++h)
+                    for (long long i = 0; i < per_x; ++i) run(START + MERGE + (h ? t - t / 2 : t / 2));
+            } else {
+                for (long long i = 0; i < per_x; ++i) run(START + t);
+            }
+        }
+        return end;
+    };
+    int best = 0;
+    float best_end = schedule(0);
+    const int most = (int)std::min<long long>(row_tiles, std::min<long long>((2LL * sms - row_tiles * per_x) / per_x, MAX_PAIRS / per_x));
+    for (int c = 1; c <= 16; ++c) {                                 // sixteen candidates up to `most`
+        const int n_split = (int)((long long)most * c / 16);
+        if (n_split <= 0 || (c > 1 && n_split == (int)((long long)most * (c - 1) / 16))) continue;
+        const float end = schedule(n_split);
+        if (end < best_end * 0.97f) { best_end = end; best = n_split; }
+    }
+    memo[memo_next] = Key{max_q_len, n_kv, group, window, batch, sms, best};
+    memo_next = (memo_next + 1) % 8;
+    return best;
+}
+
 // Prompts that start at position 0, bfloat16, head_dim 64, 128 or 256, 128 % group == 0.  q, k and v are
 // rows of q_stride / kv_stride elements (token major; head h at h * hd).  v_lbo and v_sbo are the two
-// strides of the value operand's shared-memory descriptor in bytes (0: the defaults).
+// strides of the value operand's shared-memory descriptor in bytes (0: the defaults).  n_split > 0: the
+// heaviest n_split row blocks run as two halves of their keys; part_o holds n_split * n_kv * batch * 2 *
+// 128 * hd floats, part_ml n_split * n_kv * batch * 2 * 128 * 2 (n_split * n_kv * batch <= 1024).
 BROLM_API int brolm_attn_prefill_tc(const void* q, int q_stride, void* out, int out_stride, const void* cu_q,
                                     const void* k, const void* v, int kv_stride, int total_tokens, int n_kv, int group,
                                     int hd, float scale, float cap, int window, int batch, int max_q_len, int v_lbo,
-                                    int v_sbo, cudaStream_t stream) {
+                                    int v_sbo, int n_split, void* part_o, void* part_ml, cudaStream_t stream) {
     if (batch <= 0 || max_q_len <= 0) return BROLM_OK;
     if (hd != 64 && hd != 128 && hd != 256) return BROLM_ERR_BAD_SIZE;
     if (group <= 0 || BM % group != 0 || n_kv <= 0 || batch > 65535 || n_kv > 65535) return BROLM_ERR_BAD_SIZE;
     if (q_stride % 8 || kv_stride % 8 || out_stride % 8) return BROLM_ERR_ALIGNMENT;
     if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) || ((uintptr_t)out & 15)) return BROLM_ERR_ALIGNMENT;
+    const int row_tiles = (max_q_len * group + BM - 1) / BM;
+    if (n_split < 0 || n_split > row_tiles || (long long)n_split * n_kv * batch > MAX_PAIRS) return BROLM_ERR_BAD_SIZE;
+    if (n_split > 0 && (!part_o || !part_ml || ((uintptr_t)part_o & 15) || ((uintptr_t)part_ml & 7))) return BROLM_ERR_ALIGNMENT;
     CUtensorMap mq, mk, mv;
     int st = make_map(&mq, q, total_tokens, n_kv * group, hd, q_stride, group, BM / group);
     if (st) return st;
@@ -447,7 +620,8 @@ BROLM_API int brolm_attn_prefill_tc(const void* q, int q_stride, void* out, int 
     a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window;
     a.v_lbo = (uint32_t)((v_lbo > 0 ? v_lbo : 64 * 128) >> 4);      // next 64 head-size elements: the next box
     a.v_sbo = (uint32_t)((v_sbo > 0 ? v_sbo : 1024) >> 4);          // next eight keys
-    dim3 grid((max_q_len * group + BM - 1) / BM, n_kv, batch);
+    a.n_split = n_split; a.part_o = (float*)part_o; a.part_ml = (float*)part_ml;
+    dim3 grid(row_tiles + n_split, n_kv, batch);
     if (hd == 64) return launch<64>(mq, mk, mv, a, grid, stream);
     if (hd == 128) return launch<128>(mq, mk, mv, a, grid, stream);
     return launch<256>(mq, mk, mv, a, grid, stream);

@@ -533,19 +533,50 @@ def attention_prefill_tc_ok(head_dim: int, group: int) -> bool:
     return head_dim in (64, 128, 256) and group > 0 and 128 % group == 0
 
 
+def attention_prefill_tc_split(max_q_len: int, n_kv: int, group: int, window: int, batch: int) -> int:
+    """How many of the heaviest row blocks of every (sequence, kv head) the tcgen05 prompt attention cuts in
+    two along the keys (0: none): with few kv heads and a prompt of a few thousand tokens the causal blocks
+    are few and of very different lengths, and halves fill the SMs better.  The launcher's own rule."""
+    key = (max_q_len, n_kv, group, window, batch, torch.cuda.current_device())
+    got = _split_memo.get(key)
+    if got is None:
+        f = _fn("attn_tc", "brolm_attn_prefill_tc_plan", [c_int, c_int, c_int, c_int, c_int])
+        if len(_split_memo) > 64:
+            _split_memo.clear()
+        got = _split_memo[key] = int(f(max_q_len, n_kv, group, window, batch))
+    return got
+
+
+_split_memo: dict = {}
+
+
 def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
                          n_kv: int, group: int, head_dim: int, scale: float, cap: float, window: int, batch: int,
-                         max_q_len: int, v_lbo: int = 0, v_sbo: int = 0) -> None:
-    """tcgen05 attention of whole prompts that start at position 0 (bfloat16; head_dim 64, 128 or 256)."""
+                         max_q_len: int, v_lbo: int = 0, v_sbo: int = 0, n_split: Optional[int] = None) -> None:
+    """tcgen05 attention of whole prompts that start at position 0 (bfloat16; head_dim 64, 128 or 256).
+    ``n_split``: how many of the heaviest row blocks run as two halves of their keys, merged by the half
+    that finishes second (None: ``attention_prefill_tc_split`` decides)."""
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
     assert q.stride(-1) == 1 and out.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
     assert k.stride(0) == v.stride(0) and cu_q.dtype == torch.int32 and q.shape[0] == k.shape[0] == v.shape[0]
+    if n_split is None:
+        n_split = attention_prefill_tc_split(max_q_len, n_kv, group, window, batch) if PREFILL_SPLIT else 0
+    part_o = part_ml = None
+    if n_split > 0:
+        pairs = n_split * n_kv * batch
+        both = torch.empty(pairs * 2 * 128 * (head_dim + 2), dtype=torch.float32, device=q.device)
+        part_o, part_ml = both[:pairs * 2 * 128 * head_dim], both[pairs * 2 * 128 * head_dim:]
     f = _fn("attn_tc", "brolm_attn_prefill_tc", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                  c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int,
-                                                 c_int, c_int, c_void_p])
+                                                 c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cu_q), _ptr(k), _ptr(v), k.stride(0), q.shape[0],
-             n_kv, group, head_dim, scale, cap, window, batch, max_q_len, v_lbo, v_sbo, _stream()),
+             n_kv, group, head_dim, scale, cap, window, batch, max_q_len, v_lbo, v_sbo, n_split, _ptr(part_o),
+             _ptr(part_ml), _stream()),
            "attention_prefill_tc")
+
+
+# BROLM_PREFILL_SPLIT=0: the tcgen05 prompt attention never cuts a row block's keys in two
+PREFILL_SPLIT = os.environ.get("BROLM_PREFILL_SPLIT", "1") != "0"
 
 
 def attention_tc_status(reset: bool = False) -> int:
@@ -625,5 +656,5 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
 
 __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "device_sms", "wait_control", "embed_scale", "rmsnorm", "residual_rmsnorm",
            "rope_kv_write", "rope_kv_write_parts", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc2", "gemm_tc2_status", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts", "stream_rows",
-           "gemm_stream_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_tc_status", "attention_decode_mma",
+           "gemm_stream_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_prefill_tc_split", "attention_tc_status", "attention_decode_mma",
            "decode_splits", "argmax", "sample"]

@@ -17,7 +17,7 @@ import math
 
 import torch
 
-from . import (attention_decode_mma, attention_prefill_mma, attention_prefill_tc, attention_tc_status, decode_splits, gemm_tc, gemm_tc_status, residual_rmsnorm,
+from . import (attention_decode_mma, attention_prefill_mma, attention_prefill_tc, attention_prefill_tc_split, attention_tc_status, decode_splits, gemm_tc, gemm_tc_status, residual_rmsnorm,
                rmsnorm, skinny_gemm)
 
 DEV = "cuda:0"
@@ -80,17 +80,22 @@ def attn_prefill(args) -> None:
                               qkv[:, (n_q + n_kv) * hd:], n_kv=n_kv, group=n_q // n_kv, head_dim=hd,
                               scale=1 / math.sqrt(hd), cap=args.cap, window=args.window, batch=1, max_q_len=T)
 
+    # --splits: row blocks cut in two along their keys (0: the launcher's choice, -1: none)
+    n_split = None if args.splits == 0 else max(0, args.splits)
+
     def run_tc():
         attention_prefill_tc(qkv[:, :n_q * hd], out, cu, qkv[:, n_q * hd:(n_q + n_kv) * hd],
                              qkv[:, (n_q + n_kv) * hd:], n_kv=n_kv, group=n_q // n_kv, head_dim=hd,
-                             scale=1 / math.sqrt(hd), cap=args.cap, window=args.window, batch=1, max_q_len=T)
+                             scale=1 / math.sqrt(hd), cap=args.cap, window=args.window, batch=1, max_q_len=T,
+                             n_split=n_split)
 
     w = args.window or T
     keys = sum(min(p + 1, w) for p in range(T))
     flops = 4.0 * n_q * hd * keys
     for name, fn in (("tcgen05", run_tc), ("mma.sync", run)):
         ms = timed(fn, args.reps)
-        print(f"attn_prefill {name} tokens={T} window={args.window}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.1f} TFLOP/s")
+        cut = f" cut={attention_prefill_tc_split(T, n_kv, n_q // n_kv, args.window, 1) if n_split is None else n_split}" if fn is run_tc else ""
+        print(f"attn_prefill {name} tokens={T} window={args.window}{cut}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.1f} TFLOP/s")
     print("attention_tc status", attention_tc_status())
 
 

@@ -487,6 +487,56 @@ def test_attention_tc_long_prompts(n_q, n_kv, hd, window, cap, lengths):
         t += n
 
 
+@pytest.mark.parametrize("n_q,n_kv,hd,window,cap,lengths,n_split", [
+    (8, 4, 256, 0, 50.0, [2048], None),            # the launcher's own choice (it cuts: 128 blocks on 148 SMs)
+    (8, 4, 256, 0, 50.0, [1100], 9),               # every row block in two
+    (8, 4, 256, 0, 50.0, [1100], 3),               # only the three heaviest
+    (8, 4, 256, 300, 50.0, [1500], 24),            # a window: the first half of a row block ends before some rows' windows begin
+    (4, 2, 128, 0, 30.0, [700, 64, 1, 130, 333], 6),   # sequences too short for the cut ranks, and ranks with one tile
+    (4, 4, 64, 0, 0.0, [515, 900], 8),
+    (2, 1, 256, 128, 50.0, [640], 5)])
+def test_attention_tc_row_blocks_cut_in_two_along_the_keys(n_q, n_kv, hd, window, cap, lengths, n_split):
+    """The heaviest row blocks as two halves of their keys, merged by the half that finishes second.  One far
+    key per sequence (key 3, in the first half of every later row block) is made to carry almost all the
+    weight of the last rows, so a lost or mis-scaled first half shows; twice over, so the tickets must have
+    gone back to zero."""
+    g = torch.Generator().manual_seed(17 + hd)
+    T = sum(lengths)
+    group = n_q // n_kv
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * hd, generator=g)
+    t = 0
+    for n in lengths:
+        if n > 200 and (window == 0 or window > n):
+            key = qkv[t + 3, n_q * hd:n_q * hd + hd]
+            qkv[t + n - 40:t + n, :hd] = key * 0.5           # head 0 of the last rows looks at key 3
+        t += n
+    qkv = qkv.to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(hd)
+    dq = qkv.to(DEV)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=DEV)
+    kw = dict(n_kv=n_kv, group=group, head_dim=hd, scale=scale, cap=cap, window=window, batch=len(lengths),
+              max_q_len=max(lengths))
+    if n_split is None:
+        assert kernels.attention_prefill_tc_split(max(lengths), n_kv, group, window, len(lengths)) > 0
+    whole = torch.empty(T, n_q * hd, dtype=torch.bfloat16, device=DEV)
+    kernels.attention_prefill_tc(dq[:, :n_q * hd], whole, cu, dq[:, n_q * hd:(n_q + n_kv) * hd], dq[:, (n_q + n_kv) * hd:],
+                                 n_split=0, **kw)
+    for _ in range(2):
+        out = torch.full((T, n_q * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kernels.attention_prefill_tc(dq[:, :n_q * hd], out, cu, dq[:, n_q * hd:(n_q + n_kv) * hd], dq[:, (n_q + n_kv) * hd:],
+                                     n_split=n_split, **kw)
+        assert kernels.attention_tc_status() == 0
+        t = 0
+        for n in lengths:
+            s_ = qkv[t:t + n]
+            ref = _attention_oracle(s_[:, :n_q * hd], s_[:, n_q * hd:(n_q + n_kv) * hd], s_[:, (n_q + n_kv) * hd:],
+                                    n_q, n_kv, hd, scale, cap, window)
+            close(out[t:t + n], ref, torch.bfloat16, scale=float(ref.abs().max()))
+            t += n
+        # and close to the uncut kernel's result (the same products, another order of two sums)
+        assert float((out.float() - whole.float()).abs().max()) <= 2e-2 * float(whole.float().abs().max())
+
+
 def _paged_case(dtype, n_q, n_kv, hd, window, cap, lengths, page=64, special=None, seed=0, kernel="simt", splits=1):
     """Decode pass: one query per sequence over a scattered, possibly ring-shaped cache."""
     g = torch.Generator().manual_seed(seed)
