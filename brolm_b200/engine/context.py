@@ -37,6 +37,7 @@ class StepContext:
     cache_rows: list               # per key/value group: int32 [n_tokens], page * page_size + place, or -1
     host_lengths: list             # host copy of kv_len
     max_kv_len: int = 0            # an upper bound of kv_len for sizing launches (a captured graph fixes it)
+    ragged: bool = False           # decode: the lengths are far from equal (a hint for how attention cuts its work)
 
     def __post_init__(self):
         if not self.max_kv_len:

@@ -50,10 +50,15 @@ def _next_pow2(n: int) -> int:
     return 1 << max(0, (n - 1).bit_length())
 
 
+def _ragged(lengths: Sequence[int]) -> bool:
+    """Whether the longest sequence of a decode step is well beyond the mean (by a quarter)."""
+    return len(lengths) > 1 and max(lengths) * len(lengths) > 1.25 * sum(lengths)
+
+
 class _DecodeGraph:
     """One captured decode step for a padded batch size and a bound on the lengths."""
 
-    def __init__(self, engine: "Engine", rows: int, kv_cap: int):
+    def __init__(self, engine: "Engine", rows: int, kv_cap: int, ragged: bool = False):
         cache, dev = engine.cache, engine.device
         self.rows, self.kv_cap = rows, kv_cap
         self.widths = []
@@ -83,7 +88,7 @@ class _DecodeGraph:
         self.ctx = StepContext(
             mode="decode", dtype=engine.model.dtype, device=dev, cache=cache, batch=rows, n_tokens=rows, slots=[],
             positions=seg[1], tok_seq=ar[:rows].clone(), cu_q=ar, kv_len=seg[2], slots_dev=seg[3], max_q_len=1,
-            page_tables=tables, cache_rows=cache_rows, host_lengths=[], max_kv_len=kv_cap)
+            page_tables=tables, cache_rows=cache_rows, host_lengths=[], max_kv_len=kv_cap, ragged=ragged)
         self.all_rows = ar[:rows].clone()
         # an all-padding state: the warm-up pass touches no cache
         self.hv[:] = 0
@@ -267,10 +272,13 @@ class Engine:
             self._graphs_generation = self.model.generation
         rows = _next_pow2(len(plan.slots))
         kv_cap = min(max(256, _next_pow2(max(plan.new_len))), _next_pow2(self.cache.max_positions))
-        key = (rows, kv_cap)
+        # sequences of very unequal lengths get a step of their own: its attention cuts every sequence
+        # into more pieces than one round of blocks needs, so that the SMs even out what the lengths do not
+        ragged = _ragged(plan.new_len)
+        key = (rows, kv_cap, ragged)
         g = self._graphs.get(key)
         if g is None:
-            g = self._graphs[key] = _DecodeGraph(self, rows, kv_cap)
+            g = self._graphs[key] = _DecodeGraph(self, rows, kv_cap, ragged)
         return g
 
     def _plan(self, slots, tokens, want) -> _Plan:
@@ -356,5 +364,6 @@ class Engine:
         ctx = StepContext(mode=plan.mode, dtype=self.model.dtype, device=self.device, cache=cache, batch=B,
                           n_tokens=T, slots=plan.slots, positions=seg[1], tok_seq=seg[2], cu_q=seg[3],
                           kv_len=seg[4], slots_dev=seg[5], max_q_len=int(max(plan.n_new)), page_tables=page_tables,
-                          cache_rows=cache_rows, host_lengths=plan.new_len)
+                          cache_rows=cache_rows, host_lengths=plan.new_len,
+                          ragged=plan.mode == "decode" and _ragged(plan.new_len))
         return ctx, seg[0], seg[6]

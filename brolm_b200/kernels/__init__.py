@@ -589,17 +589,31 @@ def attention_tc_status(reset: bool = False) -> int:
     return f(1 if reset else 0)
 
 
-def decode_splits(batch: int, n_kv: int, max_kv_len: int, window: int, sms: Optional[int] = None) -> int:
+RAGGED_WAVES = int(os.environ.get("BROLM_RAGGED_WAVES", "5"))
+
+
+def decode_splits(batch: int, n_kv: int, max_kv_len: int, window: int, sms: Optional[int] = None,
+                  ragged: bool = False) -> int:
     """How many blocks share the keys of one (sequence, kv head): as many as make one wave of blocks
     over the SMs (a block holds an SM's shared memory alone), at least two pages per block and at
     most 40 splits (the last block's merge reads every split's partial result).
     Measured on a B200 at 8 kv-head pairs x 4: 4 splits (one wave) read 8192 keys in 54 us, 9 splits
     (two waves) in 58 us; one sequence with 4 kv heads and 8192 keys: 37 splits (148 blocks) 1.600 ms
-    per decode step of the 2B sizes against 1.632 ms with 20 splits (80 blocks)."""
+    per decode step of the 2B sizes against 1.632 ms with 20 splits (80 blocks).
+
+    ``ragged``: the sequences' lengths are far from equal.  One round of blocks then ends with the longest
+    sequence's blocks running alone, so every sequence is cut into enough pieces for ``RAGGED_WAVES``
+    rounds and the SMs even the lengths out as they take block after block.  Measured at 16 sequences of
+    1,280 to 6,400 keys and 8 kv heads (128 pairs): 1 / 2 / 4 / 6 / 8 / 12 splits 147 / 128 / 118 / 114 /
+    116 / 126 us; with equal lengths more than one round only costs (152 / 163 / 167 us for 1 / 2 / 4).
+    (Pieces of one size for all sequences, so that a short sequence is one block and a long one many,
+    were measured too: 111 to 113 us, no better than equal shares, and are not in the kernel.)"""
     sms = sms or device_sms()
     keys = min(max_kv_len, window + 63) if window > 0 else max_kv_len
     tiles = max(1, (keys + 63) // 64)
     want = max(1, sms // max(1, batch * n_kv))
+    if ragged:
+        want = max(want, -(-RAGGED_WAVES * sms // max(1, batch * n_kv)))
     return max(1, min(want, (tiles + 1) // 2, 40))
 
 

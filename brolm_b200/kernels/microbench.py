@@ -52,7 +52,9 @@ def attn_decode(args) -> None:
     out = torch.empty_like(q)
     cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
     kv_len = torch.full((B,), ctx, dtype=torch.int32, device=DEV)
-    splits = args.splits or decode_splits(B, n_kv, ctx, args.window)
+    if args.ragged:              # lengths spread evenly between a fifth of the context and all of it
+        kv_len = torch.linspace(ctx / 5, ctx, B).round().int()[torch.randperm(B, generator=torch.Generator().manual_seed(1))].to(DEV)
+    splits = args.splits or decode_splits(B, n_kv, ctx, args.window, ragged=args.ragged)
     n = B * n_q * splits
     scratch = (torch.empty(n * hd, dtype=torch.float32, device=DEV), torch.empty(n * 2, dtype=torch.float32, device=DEV))
 
@@ -63,9 +65,9 @@ def attn_decode(args) -> None:
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
     ms = timed(run, args.reps, flush)
-    keys = min(ctx, args.window) if args.window else ctx
-    nbytes = B * keys * n_kv * hd * 2 * 2
-    print(f"attn_decode batch={B} ctx={ctx} window={args.window} splits={splits}: {ms * 1e3:.1f} us, "
+    keys = int(kv_len.clamp(max=args.window).sum()) if args.window else int(kv_len.sum())
+    nbytes = keys * n_kv * hd * 2 * 2
+    print(f"attn_decode batch={B} ctx={ctx}{' ragged' if args.ragged else ''} window={args.window} splits={splits}: {ms * 1e3:.1f} us, "
           f"{nbytes / ms / 1e6:.0f} GB/s of cache read")
 
 
@@ -291,6 +293,7 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=2304)
     ap.add_argument("--scalar", type=float, default=0.0, help="query_pre_attn_scalar (0: head_dim)")
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--ragged", action="store_true", help="attn_decode: sequences of unequal lengths up to --ctx")
     ap.add_argument("--cap", type=float, default=50.0, help="soft cap of the attention scores (0: none)")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--no-tc", action="store_true", help="many-token products through the library instead of gemm_tc")

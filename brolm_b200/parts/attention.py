@@ -114,7 +114,8 @@ class Attention(Part):
     def attend_paged(self, q, out, ctx, common, k_pages, v_pages, table, ring, page):
         if self._tensor_cores(ctx) and ctx.mode == "decode" and page == 64:
             args = {k: v for k, v in common.items() if k != "max_q_len"}
-            splits = kernels.decode_splits(ctx.batch, self.n_kv, ctx.max_kv_len, self.window or 0)
+            splits = kernels.decode_splits(ctx.batch, self.n_kv, ctx.max_kv_len, self.window or 0,
+                                           ragged=getattr(ctx, "ragged", False))
             kernels.attention_decode_mma(q, out, ctx.cu_q, ctx.kv_len, k_pages, v_pages, table, ring=ring,
                                          page_size=page, n_splits=splits, **args)
         else:

@@ -21,6 +21,11 @@ def test_decode_splits_make_one_wave_and_keep_two_pages_a_block():
         for n_kv in (1, 4, 16):
             s = kernels.decode_splits(batch, n_kv, 8192, 0)
             assert 1 <= s <= 40 and (s == 1 or s * batch * n_kv <= 148)
+    # sequences of very unequal lengths: several rounds of blocks, so that the SMs even them out
+    assert kernels.decode_splits(16, 8, 8192, 0, sms=148, ragged=True) == 6       # 768 blocks, five rounds
+    assert kernels.decode_splits(16, 8, 8192, 0, sms=148) == 1
+    assert kernels.decode_splits(64, 4, 300, 0, sms=148, ragged=True) == 3        # two pages a block at least
+    assert kernels.decode_splits(3, 4, 8192, 0, sms=148, ragged=True) == 40
 
 
 def test_slices_of_k():
