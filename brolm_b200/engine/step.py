@@ -27,6 +27,7 @@ import torch
 
 from .. import kernels
 from ..cache import Cache, CacheError
+from . import debug
 from .context import StepContext
 from .model import DecoderModel
 
@@ -48,6 +49,14 @@ class _Plan:
 
 def _next_pow2(n: int) -> int:
     return 1 << max(0, (n - 1).bit_length())
+
+
+def _checked(*args) -> None:
+    """The step's arrays against the cache's bookkeeping (``BROLM_DEBUG=1``); nothing is launched if they fail."""
+    try:
+        debug.check_step(*args)
+    except debug.StepCheckError as e:
+        raise StepError(str(e)) from None
 
 
 def _ragged(lengths: Sequence[int]) -> bool:
@@ -155,6 +164,14 @@ class _DecodeGraph:
             hv[off + g * R:off + g * R + B] = cache.decode_rows(g, plan.slots, plan.old)
         if ids is not None:
             hv[self.pick_off:self.pick_off + B] = pick
+        if debug.ENABLED:
+            tables, o = [], 4 * R
+            for w in self.widths:
+                tables.append(hv[o:o + R * w].reshape(R, w))
+                o += R * w
+            _checked(cache, "decode", 1 << 62, None if ids is not None else hv[0:B], list(hv[3 * R:4 * R]), hv[R:2 * R],
+                     np.arange(R), hv[2 * R:3 * R], tables, [hv[off + g * R:off + (g + 1) * R] for g in range(len(self.widths))],
+                     None)
         self.dev.copy_(self.host, non_blocking=True)
         self.copied.record()
         if ids is not None:
@@ -336,6 +353,9 @@ class Engine:
                  np.asarray(plan.rows, dtype=np.int64)]
         parts += [t.reshape(-1) for t in tables]
         parts += [cache.write_rows(g, plan.slots, plan.old, plan.new_len) for g in range(len(tables))]
+        if debug.ENABLED:
+            _checked(cache, plan.mode, self.vocab, plan.flat, plan.slots, positions, tok_seq, np.asarray(plan.new_len),
+                     tables, parts[7 + len(tables):], np.asarray(plan.rows, dtype=np.int64))
         sizes = [p.size for p in parts]
         offs = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])
         n = int(offs[-1])

@@ -179,6 +179,22 @@ def test_two_engines_of_one_model_with_growing_positions(setups, dtype):
     large.close([b])
 
 
+@pytest.mark.parametrize("graphs", [True, False])
+def test_steps_pass_the_debug_checks(setups, monkeypatch, graphs):
+    """With the checks of BROLM_DEBUG=1 on, prompts longer than the window's ring, unequal batches one after
+    the other (slots and pages used again) and decoding across the ring's end run as ever: the checks
+    find nothing in right steps, through the captured decode step and without it."""
+    from brolm_b200.engine import debug
+    monkeypatch.setattr(debug, "ENABLED", True)
+    _, config, weights, model = setups[("B", "bfloat16")]
+    V = config["vocab_size"]
+    eng = bb.Engine(model, max_tokens=64 * 12, max_slots=3, use_graphs=graphs)
+    assert eng.use_graphs == graphs
+    run_batch_teacher_forced(eng, config, weights, random_prompts(V, [90, 7, 40], 31), [70, 1, 30], "bfloat16")
+    run_batch_teacher_forced(eng, config, weights, random_prompts(V, [33, 140], 32), [20, 130], "bfloat16")
+    assert eng.cache.live_slots == 0
+
+
 def test_random_weights_are_the_same_bits_on_the_host_and_on_the_device():
     from brolm_b200.weights.random_init import random_tensor
     for dtype in (torch.float32, torch.bfloat16):
