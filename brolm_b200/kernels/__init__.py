@@ -250,13 +250,44 @@ def skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def skinny_parts(x: torch.Tensor, weight: torch.Tensor, sms: Optional[int] = None) -> int:
-    """Into how many slices of K a few-token product is cut so that enough blocks
-    stream the weights at once (about three per SM, two passes per warp at least)."""
+    """Into how many slices of K a few-token product is cut.
+
+    A block streams 16 rows of W over its slice, three blocks share an SM, and a stream runs near the
+    memory's rate only while the SMs hold about three blocks each: with one block an SM reaches about
+    0.45 of its share, with two 0.75, with three 0.95 (the weights of a block in flight against the
+    memory's latency).  The slices decide how many blocks there are and so how full the rounds of
+    blocks are; a last round of a few blocks streams slowly and is what to avoid.  The number of
+    slices (at most 8, at least 8 blocks of 64 k each) with the shortest estimated time is taken; every
+    slice is another float copy of the output for the kernel after it to add, which counts too.
+    Measured, product + residual kernel, microseconds at 8 tokens, by slices 1 / 2 / 3 / 4:
+    2304 x 9216 (2B down) 14.4 / 12.5 / 11.8 / 14.8; 4608 x 36864 (27B down) 74.0 / 72.9 / 63.2 / 67.4;
+    3584 x 4096 (9B o) 10.7 / 11.8 / 12.2 / 12.0."""
     sms = sms or device_sms(x.device if x.is_cuda else None)
     blocks = (weight.shape[0] + 15) // 16
     kblocks = (x.shape[1] + 63) // 64
-    want = (3 * sms + blocks - 1) // blocks
-    return max(1, min(want, kblocks // 16, 8))
+    slots = 3 * sms
+    bytes_all = float(weight.shape[0]) * x.shape[1] * 2.0
+
+    def share(per_sm: float) -> float:                     # of the memory's rate, by blocks per SM
+        pts = ((0.0, 0.0), (1.0, 0.45), (2.0, 0.75), (3.0, 0.95))
+        for (x0, y0), (x1, y1) in zip(pts, pts[1:]):
+            if per_sm <= x1:
+                return y0 + (y1 - y0) * (per_sm - x0) / (x1 - x0)
+        return 0.95
+
+    best, best_cost = 1, None
+    for parts in range(1, 9):
+        if parts > 1 and kblocks // parts < 8:
+            break
+        total, left, cost = blocks * parts, blocks * parts, 0.0
+        while left > 0:
+            now = min(left, slots)
+            cost += 1.5e-6 * 6.5e12 + bytes_all * now / total / share(now / sms)      # in bytes at the full rate
+            left -= now
+        cost += (parts - 1) * x.shape[0] * weight.shape[0] * 8.0 + (parts - 1) * 0.3e-6 * 6.5e12
+        if best_cost is None or cost < best_cost * 0.98:
+            best, best_cost = parts, cost
+    return best
 
 
 def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "store",

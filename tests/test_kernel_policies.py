@@ -32,8 +32,12 @@ def test_slices_of_k():
     x = torch.empty(8, 9216, dtype=torch.bfloat16)
     down = torch.empty(2304, 9216, dtype=torch.bfloat16)
     gate_up = torch.empty(18432, 2304, dtype=torch.bfloat16)
-    assert kernels.skinny_parts(x, down) == 4                       # 144 blocks of 16 rows: four slices fill the SMs
+    assert kernels.skinny_parts(x, down, sms=148) == 3              # 144 blocks of 16 rows: three slices are one full round (432 of 444 places)
     assert kernels.skinny_parts(torch.empty(8, 2304, dtype=torch.bfloat16), gate_up) == 1
+    # 27B down: 288 blocks, three slices are nearly two full rounds; two would leave a thin second round
+    assert kernels.skinny_parts(torch.empty(8, 36864, dtype=torch.bfloat16), torch.empty(4608, 36864, dtype=torch.bfloat16), sms=148) == 3
+    # 9B o: 224 blocks and a short K: one slice, a second round is not worth its start
+    assert kernels.skinny_parts(torch.empty(16, 4096, dtype=torch.bfloat16), torch.empty(3584, 4096, dtype=torch.bfloat16), sms=148) == 1
     assert kernels.skinny_parts(torch.empty(8, 64, dtype=torch.bfloat16), torch.empty(16, 64, dtype=torch.bfloat16)) == 1
     p = kernels.gemm_stream_parts(x, down)
     assert p >= 1 and p * 18 >= 100                                  # 18 row tiles: enough (tile, slice) items for the SMs
