@@ -249,6 +249,42 @@ def skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
             x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
+def _stream_share(fill: float) -> float:
+    """Which part of the memory's rate a stream of weights reaches while an SM holds ``fill`` of the
+    blocks it has room for (their weights in flight against the memory's latency): measured with the
+    few-token product, 0.45 with one block of three, 0.75 with two, 0.95 with all three."""
+    pts = ((0.0, 0.0), (1.0 / 3, 0.45), (2.0 / 3, 0.75), (1.0, 0.95))
+    for (x0, y0), (x1, y1) in zip(pts, pts[1:]):
+        if fill <= x1:
+            return y0 + (y1 - y0) * (fill - x0) / (x1 - x0)
+    return 0.95
+
+
+def _rounds_cost(blocks: int, per_sm: int, sms: int, nbytes: float) -> float:
+    """Estimated time, in bytes at the memory's full rate, of ``blocks`` equal blocks that stream ``nbytes``
+    in all, ``per_sm`` of them fitting an SM at a time: round after round of blocks, each round at the
+    rate its fill allows, plus 1.5 us for a round's start and end."""
+    left, cost = blocks, 0.0
+    while left > 0:
+        now = min(left, per_sm * sms)
+        cost += 1.5e-6 * 6.5e12 + nbytes * now / blocks / _stream_share(now / float(per_sm * sms))
+        left -= now
+    return cost
+
+
+def skinny_rope_tiles(width: int, k: int, sms: Optional[int] = None) -> int:
+    """16-row tiles of W per block (1 or 2) for the fused q/k/v projection, which cannot be cut along K:
+    whichever fills the rounds of blocks better.  4096 rows (Gemma 2 2B): 256 blocks of one tile, three
+    to an SM; 8192 rows (9B, 27B): 512 such blocks would be one round and a thin second one, 256 blocks of
+    two tiles, two to an SM, are one round."""
+    sms = sms or device_sms()
+    tiles = (width + 15) // 16
+    if tiles % 2:
+        return 1
+    nbytes = float(width) * k * 2.0
+    return 1 if _rounds_cost(tiles, 3, sms, nbytes) <= _rounds_cost(tiles // 2, 2, sms, nbytes) else 2
+
+
 def skinny_parts(x: torch.Tensor, weight: torch.Tensor, sms: Optional[int] = None) -> int:
     """Into how many slices of K a few-token product is cut.
 
@@ -265,25 +301,12 @@ def skinny_parts(x: torch.Tensor, weight: torch.Tensor, sms: Optional[int] = Non
     sms = sms or device_sms(x.device if x.is_cuda else None)
     blocks = (weight.shape[0] + 15) // 16
     kblocks = (x.shape[1] + 63) // 64
-    slots = 3 * sms
-    bytes_all = float(weight.shape[0]) * x.shape[1] * 2.0
-
-    def share(per_sm: float) -> float:                     # of the memory's rate, by blocks per SM
-        pts = ((0.0, 0.0), (1.0, 0.45), (2.0, 0.75), (3.0, 0.95))
-        for (x0, y0), (x1, y1) in zip(pts, pts[1:]):
-            if per_sm <= x1:
-                return y0 + (y1 - y0) * (per_sm - x0) / (x1 - x0)
-        return 0.95
-
+    nbytes = float(weight.shape[0]) * x.shape[1] * 2.0
     best, best_cost = 1, None
     for parts in range(1, 9):
         if parts > 1 and kblocks // parts < 8:
             break
-        total, left, cost = blocks * parts, blocks * parts, 0.0
-        while left > 0:
-            now = min(left, slots)
-            cost += 1.5e-6 * 6.5e12 + bytes_all * now / total / share(now / sms)      # in bytes at the full rate
-            left -= now
+        cost = _rounds_cost(blocks * parts, 3, sms, nbytes)
         cost += (parts - 1) * x.shape[0] * weight.shape[0] * 8.0 + (parts - 1) * 0.3e-6 * 6.5e12
         if best_cost is None or cost < best_cost * 0.98:
             best, best_cost = parts, cost
@@ -347,7 +370,7 @@ def skinny_qkv_rope(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, po
                                                      c_void_p, c_int, c_int, c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), x.shape[0], x.shape[1],
              _ptr(positions), _ptr(cos_sin), n_q, n_kv, head_dim, _ptr(k_pages), _ptr(v_pages), _ptr(cache_rows),
-             page_size, 2 if width >= 64 * device_sms(x.device) else 1, _stream()), "skinny_qkv_rope")
+             page_size, skinny_rope_tiles(width, x.shape[1], device_sms(x.device)), _stream()), "skinny_qkv_rope")
 
 
 USE_TC_GEMM = True      # False: many-token bfloat16 products go to the library (cuBLAS) instead
@@ -700,6 +723,6 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
 
 
 __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "device_sms", "wait_control", "embed_scale", "rmsnorm", "residual_rmsnorm",
-           "rope_kv_write", "rope_kv_write_parts", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "gemm_tc", "gemm_tc2", "gemm_tc2_status", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts", "stream_rows",
+           "rope_kv_write", "rope_kv_write_parts", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "skinny_rope_tiles", "gemm_tc", "gemm_tc2", "gemm_tc2_status", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts", "stream_rows",
            "gemm_stream_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_prefill_tc_split", "attention_tc_status", "attention_decode_mma",
            "decode_splits", "argmax", "sample"]

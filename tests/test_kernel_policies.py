@@ -39,6 +39,10 @@ def test_slices_of_k():
     # 9B o: 224 blocks and a short K: one slice, a second round is not worth its start
     assert kernels.skinny_parts(torch.empty(16, 4096, dtype=torch.bfloat16), torch.empty(3584, 4096, dtype=torch.bfloat16), sms=148) == 1
     assert kernels.skinny_parts(torch.empty(8, 64, dtype=torch.bfloat16), torch.empty(16, 64, dtype=torch.bfloat16)) == 1
+    # the fused q/k/v projection cannot be cut along K: 16-row tiles per block by how full the rounds get
+    assert kernels.skinny_rope_tiles(4096, 2304, sms=148) == 1       # 2B: 256 blocks, three to an SM
+    assert kernels.skinny_rope_tiles(8192, 3584, sms=148) == 2       # 9B: 512 would be a round and a thin one; 256 of two tiles
+    assert kernels.skinny_rope_tiles(48, 64, sms=148) == 1           # an odd number of tiles
     p = kernels.gemm_stream_parts(x, down)
     assert p >= 1 and p * 18 >= 100                                  # 18 row tiles: enough (tile, slice) items for the SMs
 
