@@ -323,8 +323,9 @@ template <int EPI>
 int dispatch(const SkinnyArgs& a, int mt, cudaStream_t stream) {
     const int nt = (a.M + 7) / 8;
     if constexpr (EPI == EPI_GATED) {
-        if (nt == 1) return mt >= 4 ? launch<4, 1, EPI>(a, stream) : launch<2, 1, EPI>(a, stream);
-        return mt >= 4 ? launch<4, 2, EPI>(a, stream) : launch<2, 2, EPI>(a, stream);
+        // (a gate and an up tile per block; blocks of two pairs measured slower at every size)
+        if (nt == 1) return launch<2, 1, EPI>(a, stream);
+        return launch<2, 2, EPI>(a, stream);
     } else if constexpr (EPI == EPI_ROPE) {
         if (nt == 1) return mt >= 2 && (a.N / 16) % 2 == 0 ? launch<2, 1, EPI>(a, stream) : launch<1, 1, EPI>(a, stream);
         return mt >= 2 && (a.N / 16) % 2 == 0 ? launch<2, 2, EPI>(a, stream) : launch<1, 2, EPI>(a, stream);
@@ -338,7 +339,7 @@ int dispatch(const SkinnyArgs& a, int mt, cudaStream_t stream) {
 
 // epilogue 0: Y = X W^T (bfloat16, or float when out_f32); 1: Y = act(X Wg^T) * (X Wu^T) with
 // W = [Wg; Wu] of 2N rows; 2: Y = cap * tanh(X W^T / cap), float.  M <= 16; K a multiple of 8;
-// rows of X and W 16-byte aligned.  tiles: 16-row tiles of W per block (1, 2 or 4).
+// rows of X and W 16-byte aligned.  tiles: 16-row tiles of W per block (1, 2 or 4; epilogue 1 always takes 2).
 // ksplit > 1 (epilogue 0 only): K is cut into ksplit slices, slice s writes its float partial
 // sums at y + s * part_stride (elements); the reader adds the slices in order.
 // The fused q/k/v projection of at most 16 tokens with the rotary position encoding and the write of
