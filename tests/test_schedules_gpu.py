@@ -179,6 +179,27 @@ def test_two_engines_of_one_model_with_growing_positions(setups, dtype):
     large.close([b])
 
 
+@pytest.mark.parametrize("name,dtype", [("A", "bfloat16"), ("B", "bfloat16"), ("B", "float32")])
+def test_many_random_batches_one_after_another(setups, name, dtype):
+    """Twelve batches of one to five requests with random prompt lengths, random prefill cuts and random
+    decode lengths through one engine, every logit against the plain implementation: equal and very
+    unequal lengths in turn (both kinds of captured step), batches that shrink step by step, slots and
+    pages used again and again, lengths on both sides of the captured steps' bounds and of the ring."""
+    import random
+    _, config, weights, model = setups[(name, dtype)]
+    V = config["vocab_size"]
+    rng = random.Random(1234 + len(name) + len(dtype))
+    eng = bb.Engine(model, max_tokens=64 * 24, max_slots=5)
+    for batch in range(12):
+        n = rng.randint(1, 5)
+        lengths = [rng.choice((rng.randint(2, 40), rng.randint(40, 140), rng.randint(240, 300))) for _ in range(n)]
+        prefill = [rng.randint(1, max(1, L - rng.randint(1, 24))) for L in lengths]
+        run_batch_teacher_forced(eng, config, weights, random_prompts(V, lengths, 500 + batch), prefill, dtype)
+        assert eng.cache.live_slots == 0 and all(g.pool.held_pages == 0 for g in eng.cache.kv_groups)
+    if eng.use_graphs:
+        assert any(key[2] for key in eng._graphs) and any(not key[2] for key in eng._graphs)
+
+
 @pytest.mark.parametrize("graphs", [True, False])
 def test_steps_pass_the_debug_checks(setups, monkeypatch, graphs):
     """With the checks of BROLM_DEBUG=1 on, prompts longer than the window's ring, unequal batches one after
