@@ -72,6 +72,26 @@ def test_residual_rmsnorm(yd, wd, od, post, nxt):
         close(out, plain.rms_norm(h_ref, w2, 1e-5), od)
 
 
+@pytest.mark.parametrize("rows,hidden", [(1500, 2304), (2000, 328), (1300, 3584), (1185, 1024), (5000, 2304)])
+@pytest.mark.parametrize("post,nxt", [(True, True), (False, True), (True, False)])
+def test_residual_rmsnorm_of_a_prompts_rows(rows, hidden, post, nxt):
+    """Thousands of rows (a prompt): the form with the row in shared memory, at one and at several rounds of
+    its blocks and at widths of one to four chunks per thread."""
+    g = torch.Generator().manual_seed(rows + hidden)
+    h = torch.randn(rows, hidden, generator=g) * 5
+    y = (torch.randn(rows, hidden, generator=g) * 2).to(torch.bfloat16)
+    w1 = (torch.randn(hidden, generator=g) * 0.1).to(torch.bfloat16)
+    w2 = (torch.randn(hidden, generator=g) * 0.1).to(torch.bfloat16)
+    hd = h.clone().to(DEV)
+    out = torch.full((rows, hidden), float("nan"), dtype=torch.bfloat16, device=DEV) if nxt else None
+    kernels.residual_rmsnorm(hd, y.to(DEV), w1.to(DEV) if post else None, 1e-6, 1.0,
+                             w2.to(DEV) if nxt else None, 1e-5, 1.0, out)
+    h_ref = h.double() + (plain.rms_norm(y, w1, 1e-6) if post else y.double())
+    close(hd, h_ref, torch.float32)
+    if nxt:
+        close(out, plain.rms_norm(h_ref, w2, 1e-5), torch.bfloat16)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
 def test_gated_act(dtype, act):
